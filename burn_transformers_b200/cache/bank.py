@@ -108,9 +108,11 @@ class CacheBank:
                 table_len = min(self.table_width, pages_for(spec.window))
                 n_pages = min(budget_pages, config.max_slots * table_len)
             shape = (len(entries), n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
+            # (a group without values keeps an empty value pool, so that every group has the same two fields)
+            v_shape = shape if spec.has_values else (len(entries), 0, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
             group = KvGroup(spec, entries, table_len, _PageBooks(self, len(self.groups), n_pages),
                             torch.zeros(shape, dtype=kv_dtype, device=self.device),
-                            torch.zeros(shape, dtype=kv_dtype, device=self.device))
+                            torch.zeros(v_shape, dtype=kv_dtype, device=self.device))
             for layer, entry in enumerate(entries):
                 self._entry_group[entry] = (len(self.groups), layer)
             self.groups.append(group)

@@ -10,10 +10,13 @@ PAGE_SIZE = 64  # tokens per page; the kernels' page_size
 
 @dataclasses.dataclass(frozen=True)
 class KvSpec:
-    """Keys and values per position: all of them (`window` None) or the last `window`."""
+    """Keys and values per position: all of them (`window` None) or the last `window`.  `has_values` False: one row
+    per position and key head only (a layer whose values are read out of the same rows, such as a latent that is both
+    key and value); the group then has no value pool."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    has_values: bool = True
 
     def __post_init__(self):
         if self.n_kv_heads <= 0 or self.head_dim <= 0:

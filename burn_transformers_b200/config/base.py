@@ -47,6 +47,8 @@ def detect_model_type(data: dict) -> str:
             if isinstance(inner, dict) and "model_type" in inner:
                 value = inner["model_type"]
                 break
+    if value is None and isinstance(data.get("architecture"), str):
+        value = data["architecture"]            # (configurations that name their design under `architecture`)
     if not isinstance(value, str):
         raise ConfigError("config", "model_type", "missing or not a string")
     return value

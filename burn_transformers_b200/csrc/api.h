@@ -14,7 +14,7 @@ int bt_tensor_map_2d_bf16(void* out, const void* base, unsigned long long rows, 
                           unsigned long long row_stride, unsigned box_rows);
 
 int bt_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int n_tokens,
-             int width, int vocab, int n_positions, int dtype, int* status, cudaStream_t stream);
+             int width, int vocab, int n_positions, float scale, int dtype, int* status, cudaStream_t stream);
 
 int bt_layernorm(const float* x, const int* rows, const float* gamma, const float* beta, void* out, int n_rows,
                  int width, float eps, int out_dtype, cudaStream_t stream);
@@ -82,6 +82,31 @@ int bt_linear_skinny_supports(int M, int N, int K, int w_is_nk, int fuse_ln);
 int bt_linear_skinny(const void* a, const float* x32, const int* rows, const float* gamma, const float* beta, float eps,
                      const void* w, const float* bias, const float* residual, void* out, int M, int N, int K,
                      int w_is_nk, int act, int out_is_f32, int split, cudaStream_t stream);
+// Attention over a latent cache (csrc/latent_attention.cu), the decayed linear recurrence (csrc/lightning.cu) and the
+// row-wise kernels between products (csrc/rowwise.cu).
+int bt_latent_append(const void* src, long long row_stride, const float* norm_weight, float eps, const int* positions,
+                     const int* token_seq, const float* inv_freq, int rot_dims, const int* table, int table_stride,
+                     int table_len, int page_size, void* pool, int n_tokens, int rank, int rot, int dtype,
+                     cudaStream_t stream);
+int bt_head_linear(const void* a, long long a_row_stride, int a_head_stride, const void* w, void* out,
+                   long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
+                   int gate_head_stride, int n_tokens, int n_heads, int K, int N, int dtype, cudaStream_t stream);
+long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank, int n_splits);
+int bt_latent_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
+                        int table_len, int page_size, const int* seq_start, const int* past_len, const float* sink,
+                        void* out, long long out_row_stride, float* part, int n_tokens, int n_seqs, int max_new,
+                        int n_heads, int rank, int rot, float scale, int n_splits, int dtype, cudaStream_t stream);
+int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
+                      const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
+                      int n_seqs, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream);
+int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate, int gate_dtype,
+               long long gate_row_stride, void* out, int out_dtype, long long out_row_stride, int n_rows, int width,
+               float eps, cudaStream_t stream);
+int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
+                          long long dst_row_stride, int dst_vec_stride, const int* positions, const float* inv_freq,
+                          int n_tokens, int n_vecs, int len, int dims, int dtype, cudaStream_t stream);
+int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, int dtype, cudaStream_t stream);
+int bt_scale(float* x, long long n, float scale, cudaStream_t stream);
 int bt_logit_edits(float* logits, long long row_stride, const int* rows, const int* tokens, const float* vals,
                    int n_edits, int vocab, cudaStream_t stream);
 }

@@ -1,5 +1,5 @@
-// Token embedding with an optional learned position table: x[t] = wte[id[t]] (+ wpe[pos[t]]).
-// The sum is formed in 32-bit and written to the 32-bit residual stream.
+// Token embedding with an optional learned position table: x[t] = (wte[id[t]] (+ wpe[pos[t]])) * scale.
+// The sum and the scaling are formed in 32-bit and written to the 32-bit residual stream.
 #include "common.cuh"
 
 namespace bt {
@@ -7,7 +7,7 @@ namespace bt {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ wte, const T* __restrict__ wpe, float* __restrict__ out,
-                             int width, int vocab, int n_positions, int* __restrict__ status) {
+                             int width, int vocab, int n_positions, float scale, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -24,26 +24,26 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = to_float(e[c]);
     if (p) v += to_float(p[c]);
-    out[(long long)t * width + c] = v;
+    out[(long long)t * width + c] = v * scale;
   }
 }
 
 }  // namespace bt
 
 extern "C" int bt_embed(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out,
-                        int n_tokens, int width, int vocab, int n_positions, int dtype, int* status,
-                        cudaStream_t stream) {
+                        int n_tokens, int width, int vocab, int n_positions, float scale, int dtype,
+                        int* status, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_tokens >= 0 && width > 0 && vocab > 0, "embed: bad sizes n_tokens=%d width=%d vocab=%d", n_tokens, width, vocab);
   if (n_tokens == 0) return 0;
   const int threads = width >= 256 ? 256 : 128;
   if (dtype == kF32)
     BT_PDL_OK("embed", launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 1, tokens, positions,
-                                  (const float*)wte, (const float*)wpe, out, width, vocab, n_positions, status));
+                                  (const float*)wte, (const float*)wpe, out, width, vocab, n_positions, scale, status));
   else if (dtype == kBF16)
     BT_PDL_OK("embed", launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 1, tokens,
                                   positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, width, vocab,
-                                  n_positions, status));
+                                  n_positions, scale, status));
   else
     return fail("embed: unknown dtype %d", dtype);
   return 0;

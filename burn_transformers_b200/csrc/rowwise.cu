@@ -1,0 +1,164 @@
+// Small row-wise kernels between the products: RMS norm (with an optional sigmoid gate), the interleaved rotation,
+// the gated activation of a feed-forward, a scale.  All arithmetic is 32-bit; results are rounded once.
+#include "common.cuh"
+
+namespace bt {
+
+// out[r, c] = x[r, c] / sqrt(mean_c(x[r]^2) + eps) * weight[c]  (* sigmoid(gate[r, c]) if gate)
+template <typename TIn, typename TGate, typename TOut>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* __restrict__ weight,
+               const TGate* __restrict__ gate, long long gate_row_stride, TOut* __restrict__ out,
+               long long out_row_stride, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const TIn* src = x + (long long)r * x_row_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float(src[c]);
+    ss += v * v;
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = to_float(src[c]) * inv * weight[c];
+    if (gate) v *= 1.f / (1.f + expf(-to_float(gate[(long long)r * gate_row_stride + c])));
+    out[(long long)r * out_row_stride + c] = from_float<TOut>(v);
+  }
+}
+
+// dst[t, v, :] = src[t, v, :] with the pairs (2i, 2i+1), i < dims/2, turned by positions[t] * inv_freq[i]; the
+// channels from `dims` to `len` are copied.  src and dst may be the same memory.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rotary_interleaved_kernel(const T* src, long long src_row_stride, int src_vec_stride, T* dst, long long dst_row_stride,
+                          int dst_vec_stride, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                          int n_vecs, int len, int dims) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  const int half = dims / 2, units = half + (len - dims);   // a unit: one pair, or one copied channel
+  for (int i = threadIdx.x; i < n_vecs * units; i += blockDim.x) {
+    const int v = i / units, u = i - v * units;
+    const T* s = src + (long long)t * src_row_stride + (long long)v * src_vec_stride;
+    T* d = dst + (long long)t * dst_row_stride + (long long)v * dst_vec_stride;
+    if (u < half) {
+      float sn, cs;
+      sincosf(pos * inv_freq[u], &sn, &cs);
+      const float a = to_float(s[2 * u]), b = to_float(s[2 * u + 1]);
+      d[2 * u] = from_float<T>(a * cs - b * sn);
+      d[2 * u + 1] = from_float<T>(b * cs + a * sn);
+    } else {
+      d[dims + (u - half)] = s[dims + (u - half)];
+    }
+  }
+}
+
+// out[r, j] = act(x[r, j]) * x[r, inner + j]
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long n_rows, int inner, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = n_rows * inner;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / inner;
+    const int j = (int)(i - r * inner);
+    const float g = to_float(x[r * 2 * inner + j]), u = to_float(x[r * 2 * inner + inner + j]);
+    out[i] = from_float<T>(apply_activation(g, act) * u);
+  }
+}
+
+__global__ void __launch_bounds__(256) scale_kernel(float* __restrict__ x, long long n, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] *= scale;
+}
+
+template <typename TIn, typename TGate>
+static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGate* gate, long long gs, void* out,
+                          long long os, int n_rows, int width, float eps, int out_dtype, cudaStream_t stream) {
+  const int threads = width >= 1024 ? 256 : 128;
+  if (out_dtype == kF32)
+    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, float>, dim3(n_rows), dim3(threads), 0, stream, 1, x, xs, w,
+                                    gate, gs, (float*)out, os, width, eps));
+  else
+    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, __nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 1, x,
+                                    xs, w, gate, gs, (__nv_bfloat16*)out, os, width, eps));
+  return 0;
+}
+
+}  // namespace bt
+
+extern "C" int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate,
+                          int gate_dtype, long long gate_row_stride, void* out, int out_dtype, long long out_row_stride,
+                          int n_rows, int width, float eps, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
+  BT_CHECK((x_dtype == kF32 || x_dtype == kBF16) && (out_dtype == kF32 || out_dtype == kBF16) &&
+           (gate == nullptr || gate_dtype == kF32 || gate_dtype == kBF16), "rmsnorm: unknown dtype");
+  if (n_rows == 0) return 0;
+  const bool gate_bf16 = gate != nullptr && gate_dtype == kBF16;
+  if (x_dtype == kF32 && !gate_bf16)
+    return launch_rmsnorm((const float*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out, out_row_stride,
+                          n_rows, width, eps, out_dtype, stream);
+  if (x_dtype == kF32)
+    return launch_rmsnorm((const float*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
+                          out_row_stride, n_rows, width, eps, out_dtype, stream);
+  if (!gate_bf16)
+    return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out,
+                          out_row_stride, n_rows, width, eps, out_dtype, stream);
+  return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
+                        out_row_stride, n_rows, width, eps, out_dtype, stream);
+}
+
+extern "C" int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
+                                     long long dst_row_stride, int dst_vec_stride, const int* positions,
+                                     const float* inv_freq, int n_tokens, int n_vecs, int len, int dims, int dtype,
+                                     cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_vecs > 0 && len > 0 && dims >= 0 && dims <= len && dims % 2 == 0,
+           "rotary_interleaved: bad sizes vectors=%d len=%d dims=%d", n_vecs, len, dims);
+  if (n_tokens == 0) return 0;
+  if (dtype == kF32)
+    BT_PDL_OK("rotary_interleaved", launch_pdl(rotary_interleaved_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                                               (const float*)src, src_row_stride, src_vec_stride, (float*)dst,
+                                               dst_row_stride, dst_vec_stride, positions, inv_freq, n_vecs, len, dims));
+  else if (dtype == kBF16)
+    BT_PDL_OK("rotary_interleaved",
+              launch_pdl(rotary_interleaved_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                         (const __nv_bfloat16*)src, src_row_stride, src_vec_stride, (__nv_bfloat16*)dst, dst_row_stride,
+                         dst_vec_stride, positions, inv_freq, n_vecs, len, dims));
+  else
+    return fail("rotary_interleaved: unknown dtype %d", dtype);
+  return 0;
+}
+
+extern "C" int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, int dtype,
+                                   cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && inner > 0, "gated_activation: bad sizes rows=%lld inner=%d", n_rows, inner);
+  if (n_rows == 0) return 0;
+  const long long total = n_rows * inner;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == kF32)
+    BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1,
+                                             (const float*)x, (float*)out, n_rows, inner, act));
+  else if (dtype == kBF16)
+    BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1,
+                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act));
+  else
+    return fail("gated_activation: unknown dtype %d", dtype);
+  return 0;
+}
+
+extern "C" int bt_scale(float* x, long long n, float scale, cudaStream_t stream) {
+  using namespace bt;
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  BT_PDL_OK("scale", launch_pdl(scale_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, n, scale));
+  return 0;
+}

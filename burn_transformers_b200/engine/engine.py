@@ -21,7 +21,7 @@ from ..cache import CacheBank, CacheConfig, PAGE_SIZE
 from ..config.registry import config_from_folder
 from ..errors import CacheError, KernelError, ShapeError
 from ..weights.loader import COMPUTE_DTYPES, load_weights
-from .model import ModelPlan
+from .model import UNBOUNDED_CONTEXT, ModelPlan
 from .step import StepBuilder, StepContext, StepEntry
 
 
@@ -66,6 +66,10 @@ class Engine:
         arch, config = config_from_folder(Path(folder))
         plan = arch.build(config)
         tensors, report = load_weights(folder, plan.weights, dtype, torch.device(device))
+        if max_context is None and plan.max_context >= UNBOUNDED_CONTEXT:
+            # a model without a position table: no sequence outgrows the cache, so the page tables need be no longer
+            # than that (4,096 positions when the caller gives no size at all)
+            max_context = -(-(max_tokens or 4096) // PAGE_SIZE) * PAGE_SIZE
         max_context = min(max_context or plan.max_context, plan.max_context)
         max_tokens = max_tokens or max_context
         cache_config = CacheConfig(max_tokens=max_tokens, max_slots=max_slots or max(1, -(-max_tokens // PAGE_SIZE)),

@@ -15,6 +15,10 @@ from ..parts.base import Block, Norm, Part, PositionEncoding
 from ..weights.spec import TensorSpec, WeightPlan
 
 
+# `max_context` of a model whose positions have no table to run out of (positions stay exact as 32-bit floats)
+UNBOUNDED_CONTEXT = 1 << 24
+
+
 @dataclasses.dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order: which block runs, and whose cache it uses.

@@ -31,6 +31,7 @@ def library() -> ctypes.CDLL:
             raise KernelError(f"cannot load the CUDA kernel library {path}: {error}") from None
         lib.bt_last_error.restype = ctypes.c_char_p
         lib.bt_attention_decode_scratch_floats.restype = c_longlong
+        lib.bt_latent_attention_scratch_floats.restype = c_longlong
         lib.bt_launch_count.restype = c_longlong
         if lib.bt_abi_version() != 1:
             raise KernelError(f"{path} has an unexpected interface version")
@@ -47,7 +48,7 @@ class KernelProfile:
     CUDA graph cannot be timed this way: profile steps that run their kernels directly."""
 
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
-            "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats")
+            "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats")
 
     def __init__(self):
         self.records = []          # (name, start event, stop event, flops, bytes)
@@ -173,8 +174,8 @@ def _code(dtype: torch.dtype) -> int:
 
 # --------------------------------------------------------------------------------------------
 
-def embed(tokens, positions, wte, wpe, out, status=None):
-    """out[t] = wte[tokens[t]] (+ wpe[positions[t]]) into the 32-bit residual stream."""
+def embed(tokens, positions, wte, wpe, out, status=None, scale: float = 1.0):
+    """out[t] = (wte[tokens[t]] (+ wpe[positions[t]])) * scale into the 32-bit residual stream."""
     n = tokens.shape[0]
     vocab, width = wte.shape
     _need(tokens, "tokens", torch.int32, (n,))
@@ -189,8 +190,8 @@ def embed(tokens, positions, wte, wpe, out, status=None):
         raise ShapeError(f"out: {out.shape[0]} rows for {n} tokens")
     _work(0.0, n * width * (wte.element_size() * (2 if wpe is not None else 1) + 4))
     _check(library().bt_embed(_ptr(tokens), _ptr(positions if wpe is not None else None), _ptr(wte), _ptr(wpe), _ptr(out),
-                              c_int(n), c_int(width), c_int(vocab), c_int(n_pos), c_int(_code(wte.dtype)),
-                              _ptr(status), _stream()))
+                              c_int(n), c_int(width), c_int(vocab), c_int(n_pos), c_float(scale),
+                              c_int(_code(wte.dtype)), _ptr(status), _stream()))
 
 
 def layernorm(x, gamma, beta, out, eps: float, rows=None, n_rows=None):
@@ -636,3 +637,156 @@ def logit_edits(logits, rows, tokens, vals, n_edits):
     _need(logits, "logits", torch.float32)
     _check(library().bt_logit_edits(_ptr(logits), c_longlong(logits.stride(0)), _ptr(rows), _ptr(tokens), _ptr(vals),
                                     c_int(n_edits), c_int(logits.shape[1]), _stream()))
+
+
+# ---- attention over a latent cache, the decayed linear recurrence, row-wise kernels ---------------------------
+
+def latent_append(src, norm_weight, eps, positions, token_seq, inv_freq, rot_dims, table, table_len, pool, n_tokens,
+                  rank, rot):
+    """Files the new tokens' latent rows: `src` [tokens, rank + rot] (a view whose rows may lie `stride(0)` apart, the
+    channels contiguous) is RMS-normed over its first `rank` channels (times `norm_weight`), its last `rot` channels are
+    turned pairwise by the token's position (the first `rot_dims` of them), and both go to `pool`
+    [pages, PAGE_SIZE, rank + rot]."""
+    if src.dim() != 2 or src.shape[1] != rank + rot or src.stride(1) != 1 or not src.is_cuda:
+        raise ShapeError(f"latent_append: src must be a device view [tokens, {rank + rot}] with contiguous channels")
+    _need(pool, "pool", src.dtype, (None, PAGE_SIZE, rank + rot))
+    _need(norm_weight, "norm_weight", torch.float32, (rank,))
+    _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rot_dims // 2:
+        raise ShapeError(f"latent_append: {inv_freq.numel()} frequencies for {rot_dims} rotated channels")
+    _need(table, "table", torch.int32)
+    _work(0.0, 2.0 * n_tokens * (rank + rot) * src.element_size())
+    _check(library().bt_latent_append(_ptr(src), c_longlong(src.stride(0)), _ptr(norm_weight), c_float(eps),
+                                      _ptr(positions), _ptr(token_seq), _ptr(inv_freq), c_int(rot_dims), _ptr(table),
+                                      c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(pool),
+                                      c_int(n_tokens), c_int(rank), c_int(rot), c_int(_code(src.dtype)), _stream()))
+
+
+def _head_view(t, name, n_heads, width):
+    """(row stride, head stride) of a view [tokens, heads, width] whose channels are contiguous."""
+    if t.dim() != 3 or t.shape[1] != n_heads or t.shape[2] != width or t.stride(2) != 1 or not t.is_cuda:
+        raise ShapeError(f"{name}: expected a device view [tokens, {n_heads}, {width}] with contiguous channels, found "
+                         f"{list(t.shape)} with strides {list(t.stride())}")
+    return t.stride(0), t.stride(1)
+
+
+def head_linear(a, w, out, *, n_tokens, gate=None):
+    """out[t, h, :] = a[t, h, :] @ w[h]  (times sigmoid(gate[t, h, :]) if `gate`), sums in 32-bit.
+
+    a: view [tokens, heads, K]; w: [heads, K, N] contiguous; out and gate: views [tokens, heads, N]."""
+    n_heads, k, n = w.shape
+    _need(w, "w", (torch.float32, torch.bfloat16), (n_heads, k, n))
+    a_rs, a_hs = _head_view(a, "a", n_heads, k)
+    o_rs, o_hs = _head_view(out, "out", n_heads, n)
+    g_rs = g_hs = 0
+    if gate is not None:
+        g_rs, g_hs = _head_view(gate, "gate", n_heads, n)
+    for name, t in (("a", a), ("out", out)) + ((("gate", gate),) if gate is not None else ()):
+        if t.dtype is not w.dtype:
+            raise ShapeError(f"head_linear: {name} is {t.dtype}, the weights are {w.dtype}")
+        if t.shape[0] < n_tokens:
+            raise ShapeError(f"head_linear: {n_tokens} tokens asked of {name}[{t.shape[0]}]")
+    _work(2.0 * n_tokens * n_heads * k * n, (n_tokens * n_heads * (k + n) + n_heads * k * n) * w.element_size())
+    _check(library().bt_head_linear(_ptr(a), c_longlong(a_rs), c_int(a_hs), _ptr(w), _ptr(out), c_longlong(o_rs),
+                                    c_int(o_hs), _ptr(gate), c_longlong(g_rs), c_int(g_hs), c_int(n_tokens),
+                                    c_int(n_heads), c_int(k), c_int(n), c_int(_code(w.dtype)), _stream()))
+
+
+def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:
+    return int(library().bt_latent_attention_scratch_floats(c_int(n_tokens), c_int(n_heads), c_int(rank), c_int(n_splits)))
+
+
+def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_tokens, n_seqs, max_new, n_heads, rank,
+                     rot, scale, sink=None, n_splits=1, scratch=None):
+    """Causal attention of the step's tokens over their sequences' latent pages.
+
+    q: [tokens, heads * (rank + rot)] (per head: the query carried into the latent space, then its rotated part);
+    pool: [pages, PAGE_SIZE, rank + rot]; out: [tokens, heads * rank] = softmax-weighted sums of the latent rows.
+    `sink` [heads] (32-bit) adds exp(sink_h) to head h's denominator.  With `n_splits` > 1 the keys of a row tile are
+    cut into that many runs whose partial results meet in `scratch` (32-bit, latent_attention_scratch_floats)."""
+    dk = rank + rot
+    _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * dk))
+    _need(out, "out", q.dtype, (None, n_heads * rank))
+    _need(pool, "pool", q.dtype, (None, PAGE_SIZE, dk))
+    _need(table, "table", torch.int32)
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
+    if q.shape[0] < n_tokens or out.shape[0] < n_tokens:
+        raise ShapeError(f"latent_attention: {n_tokens} tokens asked of q[{q.shape[0]}] and out[{out.shape[0]}]")
+    if n_splits > 1:
+        need = latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise ShapeError(f"latent_attention: {n_splits} splits need {need} floats of scratch")
+    _check(library().bt_latent_attention(
+        _ptr(q), c_longlong(q.shape[1]), _ptr(pool), _ptr(table), c_int(table.shape[1]), c_int(table_len),
+        c_int(PAGE_SIZE), _ptr(seq_start), _ptr(past_len), _ptr(sink), _ptr(out), c_longlong(out.shape[1]),
+        _ptr(scratch if n_splits > 1 else None), c_int(n_tokens), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(_code(q.dtype)), _stream()))
+
+
+def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, out, *, n_seqs, n_heads, dim, vdim):
+    """Runs S <- decay_h S + k v^T, o = S^T q over the step's tokens of every sequence, with q, k, v = x * sigmoid(x) of
+    the channels at `q_off`, `k_off`, `v_off` of the rows of `proj`.  state: [slots, heads, dim, vdim] 32-bit, read and
+    written at the rows `slots[seq]`; out: [tokens, heads * vdim] 32-bit."""
+    _need(proj, "proj", (torch.float32, torch.bfloat16))
+    _need(state, "state", torch.float32, (None, n_heads, dim, vdim))
+    _need(decay, "decay", torch.float32, (n_heads,))
+    _need(out, "out", torch.float32, (None, n_heads * vdim))
+    if max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
+        raise ShapeError("lightning_scan: the channel offsets leave the rows of proj")
+    _check(library().bt_lightning_scan(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
+                                       _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay), _ptr(out),
+                                       c_longlong(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
+                                       c_int(_code(proj.dtype)), _stream()))
+
+
+def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None):
+    """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * weight  (* sigmoid(gate[r]) if `gate`), in 32-bit.  x, gate and out are
+    2-D views with contiguous channels (rows may lie further apart); 32-bit or bfloat16 each."""
+    width = weight.shape[0]
+    _need(weight, "weight", torch.float32, (width,))
+    for name, t in (("x", x), ("out", out)) + ((("gate", gate),) if gate is not None else ()):
+        if t.dim() != 2 or t.shape[1] != width or t.stride(1) != 1 or not t.is_cuda or t.shape[0] < n_rows:
+            raise ShapeError(f"rmsnorm: {name} must be a device view [>= {n_rows}, {width}] with contiguous channels")
+    _work(0.0, n_rows * width * (x.element_size() + out.element_size()))
+    _check(library().bt_rmsnorm(_ptr(x), c_int(_code(x.dtype)), c_longlong(x.stride(0)), _ptr(weight), _ptr(gate),
+                                c_int(_code(gate.dtype)) if gate is not None else c_int(0),
+                                c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), c_int(_code(out.dtype)),
+                                c_longlong(out.stride(0)), c_int(n_rows), c_int(width), c_float(eps), _stream()))
+
+
+def rotary_interleaved(src, dst, positions, inv_freq, *, n_tokens, dims):
+    """dst[t, v] = src[t, v] with the channel pairs (2i, 2i+1), i < dims/2, turned by positions[t] * inv_freq[i]
+    (angles, sines and cosines in 32-bit); channels from `dims` on are copied.  src, dst: views
+    [tokens, vectors, len] with contiguous channels; they may be the same memory."""
+    n_vecs, length = src.shape[1], src.shape[2]
+    s_rs, s_vs = _head_view(src, "src", n_vecs, length)
+    d_rs, d_vs = _head_view(dst, "dst", n_vecs, length)
+    if src.dtype is not dst.dtype:
+        raise ShapeError(f"rotary_interleaved: src is {src.dtype}, dst {dst.dtype}")
+    _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < dims // 2:
+        raise ShapeError(f"rotary_interleaved: {inv_freq.numel()} frequencies for {dims} rotated channels")
+    _check(library().bt_rotary_interleaved(_ptr(src), c_longlong(s_rs), c_int(s_vs), _ptr(dst), c_longlong(d_rs),
+                                           c_int(d_vs), _ptr(positions), _ptr(inv_freq), c_int(n_tokens), c_int(n_vecs),
+                                           c_int(length), c_int(dims), c_int(_code(src.dtype)), _stream()))
+
+
+def gated_activation(x, out, *, n_rows, activation):
+    """out[r, j] = act(x[r, j]) * x[r, inner + j] for x [rows, 2 * inner], in 32-bit, rounded once."""
+    inner = out.shape[1]
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, 2 * inner))
+    _need(out, "out", x.dtype, (None, inner))
+    if activation not in ACTIVATIONS:
+        raise ShapeError(f"gated_activation: unknown activation {activation!r}")
+    if x.shape[0] < n_rows or out.shape[0] < n_rows:
+        raise ShapeError(f"gated_activation: {n_rows} rows asked of x[{x.shape[0]}] and out[{out.shape[0]}]")
+    _work(0.0, 3.0 * n_rows * inner * x.element_size())
+    _check(library().bt_gated_activation(_ptr(x), _ptr(out), c_longlong(n_rows), c_int(inner),
+                                         c_int(ACTIVATIONS[activation]), c_int(_code(x.dtype)), _stream()))
+
+
+def scale_(x, factor: float):
+    """x *= factor for a contiguous 32-bit tensor."""
+    _need(x, "x", torch.float32)
+    _check(library().bt_scale(_ptr(x), c_longlong(x.numel()), c_float(factor), _stream()))

@@ -1,2 +1,3 @@
 """Architectures register themselves on import."""
 from . import gpt2  # noqa: F401
+from . import sovozen  # noqa: F401

@@ -6,13 +6,19 @@ from .base import Block, FeedForward, Mixer, Norm
 
 class PreNormBlock(Block):
     """x + mixer(norm1(x)), then y + feed_forward(norm2(y)); no post-norms
-    (src/models/gpt2/model.rs:218-270 of the reference)."""
+    (src/models/gpt2/model.rs:218-270 of the reference).  A layer without a feed-forward (`norm2` and `feed_forward`
+    None) has the first sublayer only."""
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None = None, feed_forward: FeedForward | None = None):
+        if (norm2 is None) != (feed_forward is None):
+            raise ValueError("a block has both a second norm and a feed-forward, or neither")
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
     def parts(self):
-        return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "feed_forward": self.feed_forward}
+        found = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.feed_forward is not None:
+            found.update({"norm2": self.norm2, "feed_forward": self.feed_forward})
+        return found
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -24,5 +30,7 @@ class PreNormBlock(Block):
     def forward(self, ctx, residual, entry, owns_cache=True):
         x = self.norm1.forward(ctx, residual, ctx.dtype, lazy=self.mixer.accepts_lazy_norm)
         self.mixer.forward(ctx, x, residual, entry, owns_cache)
+        if self.feed_forward is None:
+            return
         x = self.norm2.forward(ctx, residual, ctx.dtype, lazy=self.feed_forward.accepts_lazy_norm)
         self.feed_forward.forward(ctx, x, residual)

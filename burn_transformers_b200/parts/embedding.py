@@ -10,10 +10,11 @@ from .linear import linear
 
 
 class TokenEmbedding(Part):
-    """x0[t] = table[id[t]] (+ the position table's row when the position encoding is a learned one)."""
+    """x0[t] = (table[id[t]] (+ the position table's row when the position encoding is a learned one)) * scale,
+    the scaling in 32-bit."""
 
-    def __init__(self, vocab: int, width: int, init_std: float = 0.02):
-        self.vocab, self.width, self.init_std = vocab, width, init_std
+    def __init__(self, vocab: int, width: int, init_std: float = 0.02, scale: float = 1.0):
+        self.vocab, self.width, self.init_std, self.scale = vocab, width, init_std, float(scale)
 
     def specs(self):
         return {"weight": TensorSpec((self.vocab, self.width), MATRIX, ("normal", self.init_std))}
@@ -22,9 +23,12 @@ class TokenEmbedding(Part):
         table = positions_part.t_weight if getattr(positions_part, "adds_to_embedding", False) else None
         program = getattr(ctx, "program", None)
         if program is not None:
+            if self.scale != 1.0:
+                from ..engine.program import ProgramUnsupported
+                raise ProgramUnsupported("a scaled embedding has no phase in the fused step")
             program.add_embed(ctx.tokens, ctx.positions if table is not None else None, self.t_weight, table, out32)
             return
-        kernels.embed(ctx.tokens, ctx.positions, self.t_weight, table, out32, status=None)
+        kernels.embed(ctx.tokens, ctx.positions, self.t_weight, table, out32, status=None, scale=self.scale)
 
 
 class TiedReadout(Part):
@@ -39,4 +43,27 @@ class TiedReadout(Part):
     def forward(self, ctx, h, n_rows: int):
         logits = ctx.ws.take((n_rows, self.embedding.vocab), torch.float32)
         linear(ctx, h, self.embedding.t_weight, None, logits, m=n_rows, w_is_nk=True)
+        return logits
+
+
+class LinearReadout(Part):
+    """logits = (h @ weight^T) * scale with a table of its own, stored [vocab, width]; no bias, 32-bit logits, the
+    scaling in 32-bit."""
+
+    accepts_lazy_norm = True
+
+    def __init__(self, vocab: int, width: int, scale: float = 1.0, init_std: float = 0.02):
+        self.vocab, self.width, self.scale, self.init_std = vocab, width, float(scale), init_std
+
+    def specs(self):
+        return {"weight": TensorSpec((self.vocab, self.width), MATRIX, ("normal", self.init_std))}
+
+    def forward(self, ctx, h, n_rows: int):
+        logits = ctx.ws.take((n_rows, self.vocab), torch.float32)
+        linear(ctx, h, self.t_weight, None, logits, m=n_rows, w_is_nk=True)
+        if self.scale != 1.0:
+            if getattr(ctx, "program", None) is not None:
+                from ..engine.program import ProgramUnsupported
+                raise ProgramUnsupported("a scaled readout has no phase in the fused step")
+            kernels.scale_(logits, self.scale)
         return logits

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 from ..weights.spec import MATRIX, VECTOR, TensorSpec
+from .. import kernels
 from .base import FeedForward
 from .linear import linear
 
@@ -39,3 +40,34 @@ class DenseFeedForward(FeedForward):
                activation=self.activation, w_is_nk=self.nk_up_weight)
         linear(ctx, hidden, self.t_down_weight, self.t_down_bias if self.has_bias else None, residual, m=n,
                residual=residual, w_is_nk=self.nk_down_weight)
+
+
+class GatedFeedForward(FeedForward):
+    """down(act(gate(x)) * up(x)), added to the residual stream; no biases.  The gate and up matrices are one product:
+    `gate_up.weight` is [2 * inner, width] (stored [out, in]: the gate's rows, then up's), `down.weight` [width, inner].
+    The activation and the product of the two halves are formed in 32-bit and rounded once."""
+
+    accepts_lazy_norm = True
+
+    def __init__(self, width: int, inner: int, activation: str = "gelu_new", *, init_std: float = 0.02,
+                 down_init_std: float | None = None):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"activation must be one of {ACTIVATIONS}, found {activation!r}")
+        self.width, self.inner, self.activation = width, inner, activation
+        self.init_std = init_std
+        self.down_init_std = init_std if down_init_std is None else down_init_std
+
+    def specs(self):
+        return {"gate_up.weight": TensorSpec((2 * self.inner, self.width), MATRIX, ("normal", self.init_std)),
+                "down.weight": TensorSpec((self.width, self.inner), MATRIX, ("normal", self.down_init_std))}
+
+    def forward(self, ctx, x, residual):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("a gated feed-forward has no phase in the fused step")
+        n = ctx.n_tokens
+        both = ctx.ws.take((n, 2 * self.inner), ctx.dtype)
+        linear(ctx, x, self.t_gate_up_weight, None, both, m=n, w_is_nk=True)
+        hidden = ctx.ws.take((n, self.inner), ctx.dtype)
+        kernels.gated_activation(both, hidden, n_rows=n, activation=self.activation)
+        linear(ctx, hidden, self.t_down_weight, None, residual, m=n, residual=residual, w_is_nk=True)

@@ -1,0 +1,137 @@
+"""Attention with a low-rank latent for keys and values."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.spec import PAGE_SIZE, CacheNeed, KvSpec
+from ..errors import ShapeError
+from ..weights.spec import MATRIX, VECTOR, TensorSpec
+from .attention import _sm_count
+from .base import Mixer
+from .linear import linear
+
+
+class LatentAttention(Mixer):
+    """Multi-head causal attention whose keys and values come from one low-rank latent per position.
+
+    With h the mixer's input, per position:
+
+        q       = W_q h                     per head [dim plain | rot_dim rotated] channels
+        [d | r] = W_dkv h                   d: kv_rank channels, r: rot_dim channels
+        c       = d / rms(d) * norm         the latent (eps inside the root)
+        r'      = rotate(r, position)       one rotated key part that all heads share
+
+    Head i has keys [W_uk,i c | r'] and values W_uv,i c; its scores are (q_plain . W_uk,i c + q_rot' . r') * scale,
+    causal, with a softmax whose denominator may also hold exp(sink_i): a learned per-head logit that competes for
+    weight but contributes nothing to the output.  The heads side by side are multiplied by sigmoid(W_g h) and projected by W_o into the residual stream.
+
+    Only [c | r'] is cached: one row of kv_rank + rot_dim per position for all heads, and it is both key and value
+    (`KvSpec(1, kv_rank + rot_dim, has_values=False)`).  The up-projections act on the query side instead
+    (csrc/latent_attention.cu): q~_i = W_uk,i^T q_plain,i meets c directly, and W_uv,i acts once on the weighted sum
+    of latents.  A layer built with `owns_latent=False` has no W_dkv; the model's run order gives it another layer's
+    cache entry, whose rows it reads with its own W_uk, W_uv, queries and everything else.
+
+    Tensors (stored [out, in]): `in.weight` = rows of W_q, then W_g, then (owner only) W_dkv; `uk.weight`
+    [heads * dim, kv_rank]; `uv.weight` [heads * vdim, kv_rank]; `latent_norm.weight` [kv_rank] (owner only); `sink`
+    [heads] (if `sink`); `out.weight` [width, heads * vdim].
+    """
+
+    accepts_lazy_norm = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
+                 positions, *, owns_latent: bool = True, sink: bool = True, init_std: float = 0.02,
+                 out_init_std: float | None = None):
+        if min(width, n_heads, dim, vdim, kv_rank) <= 0 or rot_dim < 0:
+            raise ShapeError("latent attention: sizes must be positive")
+        if kv_rank > 512:
+            raise ShapeError(f"latent attention: a latent of {kv_rank} channels exceeds the 512 the attention kernel takes")
+        if positions is None or not positions.rotates or positions.dims > rot_dim:
+            raise ShapeError("latent attention: needs a rotating position encoding over at most rot_dim channels")
+        self.width, self.n_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = width, n_heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.eps, self.positions = float(scale), float(eps), positions
+        self.owns_latent, self.has_sink = owns_latent, sink
+        self.q_width = n_heads * (dim + rot_dim)
+        self.gate_width = n_heads * vdim
+        self.latent_width = kv_rank + rot_dim
+        self.in_width = self.q_width + self.gate_width + (self.latent_width if owns_latent else 0)
+        self.init_std = init_std
+        self.out_init_std = init_std if out_init_std is None else out_init_std
+
+    def specs(self):
+        up_std = self.kv_rank ** -0.5
+        specs = {"in.weight": TensorSpec((self.in_width, self.width), MATRIX, ("normal", self.init_std)),
+                 "uk.weight": TensorSpec((self.n_heads * self.dim, self.kv_rank), MATRIX, ("normal", up_std)),
+                 "uv.weight": TensorSpec((self.n_heads * self.vdim, self.kv_rank), MATRIX, ("normal", up_std)),
+                 "out.weight": TensorSpec((self.width, self.n_heads * self.vdim), MATRIX, ("normal", self.out_init_std))}
+        if self.owns_latent:
+            specs["latent_norm.weight"] = TensorSpec((self.kv_rank,), VECTOR, ("ones",))
+        if self.has_sink:
+            specs["sink"] = TensorSpec((self.n_heads,), VECTOR, ("zeros",))
+        return specs
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        # per head [K, N] operands of the per-head products: W_uk,i as stored ([dim, kv_rank]), W_uv,i turned
+        # ([kv_rank, vdim])
+        self.uk_heads = self.t_uk_weight.view(self.n_heads, self.dim, self.kv_rank)
+        self.uv_heads = self.t_uv_weight.view(self.n_heads, self.vdim, self.kv_rank).transpose(1, 2).contiguous()
+        self.positions.inv_freq(self.t_uk_weight.device)
+
+    def cache_need(self):
+        if not self.owns_latent:
+            return CacheNeed()
+        return CacheNeed(kv=KvSpec(1, self.latent_width, None, has_values=False))
+
+    def _splits(self, ctx, rows_per_block: int) -> int:
+        """Runs the keys of a row tile are cut into: enough blocks to fill the GPU about twice, none when the step's
+        rows do that by themselves; at most one per 32 keys."""
+        hb = min(self.n_heads, rows_per_block)
+        tiles = -(-self.n_heads // hb) * -(-ctx.max_new // max(1, rows_per_block // hb)) * ctx.n_seqs
+        by_fill = -(-2 * _sm_count(ctx.ws.device) // max(1, tiles))
+        return int(max(1, min(by_fill, -(-ctx.ctx_bound // 32), 64)))
+
+    def forward(self, ctx, x, residual, entry, owns_cache=True):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("latent attention has no phase in the fused step")
+        if owns_cache != self.owns_latent:
+            raise ShapeError("latent attention: a layer with its own latent projection owns its cache entry, and a "
+                             "layer without one reads another layer's")
+        n, dtype, heads = ctx.n_tokens, ctx.dtype, self.n_heads
+        rank, rot, dk = self.kv_rank, self.rot_dim, self.latent_width
+        proj = ctx.ws.take((n, self.in_width), dtype)
+        linear(ctx, x, self.t_in_weight, None, proj, m=n, w_is_nk=True)
+        k_pool, _, group, g = ctx.cache.layer_pools(entry)
+        if group.spec.head_dim != dk or group.spec.n_kv_heads != 1:
+            raise ShapeError(f"latent attention: the cache entry holds rows of {group.spec.n_kv_heads} x "
+                             f"{group.spec.head_dim}, this layer reads rows of 1 x {dk}")
+        pool = k_pool.view(-1, PAGE_SIZE, dk)
+        table = ctx.tables[g]
+        freq = self.positions.inv_freq(proj.device)
+        if self.owns_latent:
+            kernels.latent_append(proj[:, self.q_width + self.gate_width:], self.t_latent_norm_weight, self.eps,
+                                  ctx.positions, ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool,
+                                  n, rank, rot)
+        # the queries as the latent rows meet them: per head [W_uk^T q_plain | q_rot turned]
+        q_heads = proj[:, :self.q_width].view(n, heads, self.dim + rot)
+        q_latent = ctx.ws.take((n, heads * dk), dtype)
+        q_latent_heads = q_latent.view(n, heads, dk)
+        kernels.head_linear(q_heads[:, :, :self.dim], self.uk_heads, q_latent_heads[:, :, :rank], n_tokens=n)
+        if rot:
+            self.positions.rotate_vectors(ctx, q_heads[:, :, self.dim:], q_latent_heads[:, :, rank:])
+        mixed_latent = ctx.ws.take((n, heads * rank), dtype)
+        splits = self._splits(ctx, 32 if rank <= 128 else 16)
+        scratch = None
+        if splits > 1:
+            scratch = ctx.ws.take((kernels.latent_attention_scratch_floats(n, heads, rank, splits),), torch.float32)
+        kernels.latent_attention(q_latent, mixed_latent, pool, table, group.table_len, ctx.seq_start, ctx.past_len,
+                                 n_tokens=n, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, rank=rank, rot=rot,
+                                 scale=self.scale, sink=self.t_sink if self.has_sink else None, n_splits=splits,
+                                 scratch=scratch)
+        # values: W_uv on the weighted latents, times the output gate
+        mixed = ctx.ws.take((n, self.gate_width), dtype)
+        gate = proj[:, self.q_width:self.q_width + self.gate_width].view(n, heads, self.vdim)
+        kernels.head_linear(mixed_latent.view(n, heads, rank), self.uv_heads, mixed.view(n, heads, self.vdim), n_tokens=n,
+                            gate=gate)
+        linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)

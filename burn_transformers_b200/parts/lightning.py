@@ -1,0 +1,71 @@
+"""Linear attention with a per-head decay: a recurrent state instead of cached keys."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.spec import CacheNeed, StateSpec
+from ..errors import ShapeError
+from ..weights.spec import MATRIX, VECTOR, TensorSpec
+from .base import Mixer
+from .linear import linear
+
+
+class LightningAttention(Mixer):
+    """Per head a state S (dim x vdim, 32-bit, zero for a new sequence) that every token updates and reads:
+
+        q = act(W_q h), k = act(W_k h), v = act(W_v h)       act(x) = x * sigmoid(x)
+        S_t = decay_i * S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+
+    with one decay per head and no other scale.  The heads' o_t side by side are RMS-normed together (plain weight, eps
+    inside the root), multiplied by sigmoid(W_g h) and projected by W_o into the residual stream.  The recurrence,
+    the norm and the gate run in 32-bit (csrc/lightning.cu, csrc/rowwise.cu).  The state is the layer's only cache:
+    `StateSpec("s", (heads, dim, vdim))`, one row per live sequence.
+
+    Tensors (stored [out, in]): `in.weight` = rows of W_q, W_k, W_v, W_g; `norm.weight` [heads * vdim];
+    `out.weight` [width, heads * vdim].
+    """
+
+    accepts_lazy_norm = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, vdim: int, decay, eps: float, *, init_std: float = 0.02,
+                 out_init_std: float | None = None):
+        decay = [float(d) for d in decay]
+        if min(width, n_heads, dim, vdim) <= 0 or len(decay) != n_heads:
+            raise ShapeError(f"lightning attention: {n_heads} heads need as many decays, found {len(decay)}")
+        if dim > 256:
+            raise ShapeError(f"lightning attention: {dim} key channels per head exceed the 256 the recurrence kernel takes")
+        self.width, self.n_heads, self.dim, self.vdim, self.decay, self.eps = width, n_heads, dim, vdim, decay, float(eps)
+        self.qk_width, self.v_width = n_heads * dim, n_heads * vdim
+        self.in_width = 2 * self.qk_width + 2 * self.v_width
+        self.init_std = init_std
+        self.out_init_std = init_std if out_init_std is None else out_init_std
+
+    def specs(self):
+        return {"in.weight": TensorSpec((self.in_width, self.width), MATRIX, ("normal", self.init_std)),
+                "norm.weight": TensorSpec((self.v_width,), VECTOR, ("ones",)),
+                "out.weight": TensorSpec((self.width, self.v_width), MATRIX, ("normal", self.out_init_std))}
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.decay_device = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(self.t_in_weight.device)
+
+    def cache_need(self):
+        return CacheNeed(states=(StateSpec("s", (self.n_heads, self.dim, self.vdim), torch.float32),))
+
+    def forward(self, ctx, x, residual, entry, owns_cache=True):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("lightning attention has no phase in the fused step")
+        if not owns_cache:
+            raise ShapeError("lightning attention: a recurrent state cannot be another layer's")
+        n = ctx.n_tokens
+        proj = ctx.ws.take((n, self.in_width), ctx.dtype)
+        linear(ctx, x, self.t_in_weight, None, proj, m=n, w_is_nk=True)
+        read = ctx.ws.take((n, self.v_width), torch.float32)
+        kernels.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, ctx.cache.state(entry, "s"), ctx.slots,
+                               ctx.seq_start, self.decay_device, read, n_seqs=ctx.n_seqs, n_heads=self.n_heads,
+                               dim=self.dim, vdim=self.vdim)
+        mixed = ctx.ws.take((n, self.v_width), ctx.dtype)
+        kernels.rmsnorm(read, self.t_norm_weight, mixed, self.eps, n_rows=n, gate=proj[:, 2 * self.qk_width + self.v_width:])
+        linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)

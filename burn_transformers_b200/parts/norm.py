@@ -37,3 +37,26 @@ class LayerNorm(Norm):
         out = ctx.ws.take((n, self.width), out_dtype)
         kernels.layernorm(x32, self.t_weight, self.t_bias if self.has_bias else None, out, self.eps, rows=rows, n_rows=n)
         return out
+
+
+class RmsNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * weight over the last axis, in 32-bit, eps inside the root; no shift."""
+
+    has_bias = False
+
+    def __init__(self, width: int, eps: float):
+        self.width, self.eps = width, float(eps)
+
+    def specs(self):
+        return {"weight": TensorSpec((self.width,), VECTOR, ("ones",))}
+
+    def forward(self, ctx, x32, out_dtype, rows=None, n_rows=None, lazy=False):
+        n = n_rows if n_rows is not None else ctx.n_tokens
+        return self.apply(ctx, x32, out_dtype, rows, n)
+
+    def apply(self, ctx, x32, out_dtype, rows, n):
+        if rows is not None:
+            x32 = x32.index_select(0, rows[:n].long())
+        out = ctx.ws.take((n, self.width), out_dtype)
+        kernels.rmsnorm(x32, self.t_weight, out, self.eps, n_rows=n)
+        return out

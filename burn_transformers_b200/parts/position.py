@@ -1,6 +1,9 @@
 """Position encodings."""
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from ..weights.spec import MATRIX, TensorSpec
 from .base import PositionEncoding
 
@@ -22,3 +25,40 @@ class LearnedPositions(PositionEncoding):
 
     def max_positions(self):
         return self.n_positions
+
+
+class InterleavedRotary(PositionEncoding):
+    """Turns channel pairs of query and key vectors by an angle that grows with the position: the pair (2i, 2i+1),
+    i < dims/2, of a vector at position p becomes (u cos a - v sin a, v cos a + u sin a) with a = p * base^(-2i/dims);
+    channels from `dims` on pass unchanged.  The frequencies are formed in 64-bit on the host and rounded once; angle,
+    sine and cosine are 32-bit on the device.  Owns no tensor."""
+    rotates = True
+
+    def __init__(self, dims: int, base: float):
+        if dims < 0 or dims % 2:
+            raise ValueError(f"a rotation takes an even number of channels, not {dims}")
+        self.dims, self.base = int(dims), float(base)
+        self._freq: dict = {}
+
+    def inv_freq(self, device) -> torch.Tensor:
+        """[dims / 2] 32-bit frequencies on `device` (made once per device; before any stream capture: a mixer that
+        uses this part asks for them when it is bound)."""
+        device = torch.device(device)
+        hit = self._freq.get(device)
+        if hit is None:
+            half = max(1, self.dims // 2)
+            values = [self.base ** (-2.0 * i / self.dims) if self.dims else 1.0 for i in range(half)]
+            hit = torch.tensor(values, dtype=torch.float64).to(torch.float32).to(device)
+            self._freq[device] = hit
+        return hit
+
+    def rotate_vectors(self, ctx, src, dst) -> None:
+        """dst[t, v, :] = src[t, v, :] turned by the position of token t (views [tokens, vectors, length])."""
+        kernels.rotary_interleaved(src, dst, ctx.positions, self.inv_freq(src.device), n_tokens=ctx.n_tokens,
+                                   dims=self.dims)
+
+    def rotate(self, ctx, proj, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        n = ctx.n_tokens
+        heads = n_heads + n_kv_heads              # queries and keys lie side by side, values after them
+        view = proj[:n, :heads * head_dim].view(n, heads, head_dim)
+        self.rotate_vectors(ctx, view, view)

@@ -23,7 +23,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from ..config.base import ModelConfig
+from ..config.base import ModelConfig, detect_model_type
 from ..config.registry import architecture_for
 from .safetensors_io import write_file
 from .spec import MATRIX, VECTOR, WeightPlan
@@ -117,7 +117,7 @@ def write_random_model(folder, config: ModelConfig | dict, seed: int, *, storage
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     if isinstance(config, dict):
-        arch = architecture_for(config.get("model_type", ""))
+        arch = architecture_for(detect_model_type(config))
         config = arch.config_class.from_dict(config)
     else:
         arch = architecture_for(config.model_type)
