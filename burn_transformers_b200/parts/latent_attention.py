@@ -67,7 +67,7 @@ class LatentAttention(Mixer):
         if self.owns_latent:
             specs["latent_norm.weight"] = TensorSpec((self.kv_rank,), VECTOR, ("ones",))
         if self.has_sink:
-            specs["sink"] = TensorSpec((self.n_heads,), VECTOR, ("zeros",))
+            specs["sink"] = TensorSpec((self.n_heads,), VECTOR, ("normal", 1.0))
         return specs
 
     def bind(self, tensors):
