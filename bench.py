@@ -1,6 +1,7 @@
 """Decode and prefill throughput of GPT-2 (random weights, synthetic tokens) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--points all|small] [--profile]
+    python bench.py --arch sovozen [--sizes small,medium]
 
 A step is one decode step of a batch of 8 sequences of GPT-2 small.  The run prints one JSON line: `value` is decoded
 tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the public
@@ -350,6 +351,118 @@ def run_profile(args, torch, bt, kernels, pk):
     return 0
 
 
+def sovozen(size: str) -> dict:
+    """A Sovozen of the width and depth of GPT-2 `size`: of every three layers, one with a latent of its own, one
+    decayed linear attention, one that reads the first one's latent; gated feed-forwards of the same weight count as
+    GPT-2's (3 x ff x width = 8 x width^2)."""
+    n_layer, width, heads = {"small": (12, 768, 12), "medium": (24, 1024, 16)}[size]
+    rank, rot, dim = {"small": (256, 32, 64), "medium": (512, 64, 64)}[size]
+    ff = {"small": 2048, "medium": 2816}[size]
+    mlp = {"kind": "dense", "ff": ff}
+    layers = []
+    for i in range(n_layer):
+        if i % 3 == 1:
+            mixer = {"heads": heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** -(3 + h % 6) for h in range(heads)]}
+            layers.append({"type": "lightning", "mixer": mixer, "mlp": mlp})
+            continue
+        mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+                 "rot": {"dims": rot, "base": 10000.0}}
+        if i % 3 == 2:
+            mixer["kv_from"] = i - 2
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Sovozen", "vocab": 50257, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "logit_scale": 1.0, "layers": layers}
+
+
+def run_arch_compare(args):
+    """--arch sovozen: prefill and decode throughput of a Sovozen beside the GPT-2 of the same width and depth (random
+    weights, bfloat16), and where each spends a prefill and a decode step, kernel by kernel, against the measured
+    peaks.  One JSON line; the default workload of this file is untouched."""
+    import numpy as np
+    import torch
+
+    import burn_transformers_b200 as bt
+    from burn_transformers_b200 import kernels
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: this benchmark has no CPU path"}))
+        return 1
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    report = {"arch": "sovozen", "beside": "gpt2", "dtype": "bf16", "data": "synthetic: random ids, random weights",
+              "peaks": pk, "sizes": {}}
+
+    def kernel_table(rows, steps=1):
+        return [{"kernel": r["kernel"], "launches": r["launches"] // steps, "us": round(r["ms"] * 1e3 / steps, 2),
+                 "share": round(r["share"], 4),
+                 "frac_of_bf16_peak": None if r["tflops"] is None else round(r["tflops"] / pk["bf16_tflops"], 4),
+                 "frac_of_copy_rate": None if r["gbs"] is None else round(r["gbs"] / pk["hbm_gbs"], 4)} for r in rows]
+
+    def measure(cfg, vocab):
+        engine = make_engine(cfg, bt, torch, max_tokens=64 * CONTEXT, max_slots=64, fast_weights=True)
+        out = {}
+        prompts = [rng.integers(0, vocab, PREFILL_TOKENS // 2).tolist() for _ in range(2)]
+        stats = timed_prefill(engine, prompts, torch, bt)
+        out["prefill_2x1024"] = {"ms": stats, "tokens_per_s": PREFILL_TOKENS / stats["median"] * 1e3}
+        for batch in (8, 64):
+            samples = []
+            for rep in range(2 + 5):
+                slots = [engine.new_sequence() for _ in range(batch)]
+                try:
+                    engine.step([bt.StepEntry(s, rng.integers(0, vocab, 512).tolist(), []) for s in slots])
+                    step = lambda: engine.step([bt.StepEntry(s, [int(rng.integers(0, vocab))], [0]) for s in slots])
+                    for _ in range(3):
+                        step()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    graph = engine.decode_graph(batch)
+                    torch.cuda.synchronize()
+                    a.record()
+                    for _ in range(32):
+                        graph.run()          # (the recorded step replayed on the same integers: device time only)
+                    b.record()
+                    torch.cuda.synchronize()
+                    if rep >= 2:
+                        samples.append(a.elapsed_time(b) / 32)
+                finally:
+                    for s in slots:
+                        engine.release(s)
+            st = spread(samples)
+            out[f"decode_b{batch}_ctx512"] = {"ms_per_step": st, "tokens_per_s": batch / st["median"] * 1e3}
+        # kernel by kernel, launched directly
+        for warm in range(2):
+            prompts = [rng.integers(0, vocab, PREFILL_TOKENS // 2 - 1 - warm).tolist() for _ in range(2)]
+            slots = [engine.new_sequence() for _ in prompts]
+            with kernels.KernelProfile(context_hint=PREFILL_TOKENS // 2) as prof:
+                engine.step([bt.StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+            rows = prof.summary()
+            for s in slots:
+                engine.release(s)
+        out["prefill_kernels"] = kernel_table(rows)
+        engine.use_fused_step = False
+        engine.use_graphs = False
+        slots = [engine.new_sequence() for _ in range(8)]
+        engine.step([bt.StepEntry(s, rng.integers(0, vocab, 512).tolist(), []) for s in slots])
+        step = lambda: engine.step([bt.StepEntry(s, [int(rng.integers(0, vocab))], [0]) for s in slots])
+        for _ in range(3):
+            step()
+        with kernels.KernelProfile(context_hint=520) as prof:
+            for _ in range(8):
+                step()
+        out["decode_b8_kernels"] = kernel_table(prof.summary(), steps=8)
+        for s in slots:
+            engine.release(s)
+        del engine
+        torch.cuda.empty_cache()
+        return out
+
+    with ClockSampler() as clocks:
+        for size in args.sizes.split(","):
+            report["sizes"][size] = {"sovozen": measure(sovozen(size), 50257), "gpt2": measure(gpt2(size), 50257)}
+    report["clocks"] = clocks.summary()
+    print(json.dumps(report))
+    return 0
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -478,6 +591,9 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
     parser.add_argument("--model", choices=["small", "medium", "xl"], default="small", help="the model --profile looks at")
+    parser.add_argument("--arch", choices=["gpt2", "sovozen"], default="gpt2",
+                        help="sovozen: measure a Sovozen beside the GPT-2 of equal width and depth instead (see --sizes)")
+    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen: which widths (small, medium)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "
@@ -489,6 +605,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.arch == "sovozen":
+        return run_arch_compare(args)
     return run_ours(args)
 
 

@@ -95,7 +95,9 @@ long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank
 int bt_latent_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
                         int table_len, int page_size, const int* seq_start, const int* past_len, const float* sink,
                         void* out, long long out_row_stride, float* part, int n_tokens, int n_seqs, int max_new,
-                        int n_heads, int rank, int rot, float scale, int n_splits, int dtype, cudaStream_t stream);
+                        int n_heads, int rank, int rot, float scale, int n_splits, int tensor_cores, int dtype,
+                        cudaStream_t stream);
+int bt_latent_attention_rows(int rank, int rot, int dtype, int tensor_cores);
 int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                       const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
                       int n_seqs, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream);

@@ -21,6 +21,15 @@
 
 namespace bt {
 
+// the tensor-core kernel for bfloat16 (latent_attention_mma.cu)
+int latent_attention_mma_rows();
+bool latent_attention_mma_supports(int rank, int rot);
+int launch_latent_attention_mma(const __nv_bfloat16* q, long long q_row_stride, const __nv_bfloat16* pool, const int* table,
+                                int table_stride, int table_len, int page_size, const int* seq_start, const int* past_len,
+                                const float* sink, __nv_bfloat16* out, long long out_row_stride, float* part, int n_seqs,
+                                int max_new, int n_heads, int rank, int rot, float scale, int n_splits,
+                                cudaStream_t stream);
+
 // ---- filing the latent ------------------------------------------------------------------------------------------
 
 // One block per new token.  src row: [rank latent channels | rot key channels] at `src + t * row_stride`.
@@ -314,6 +323,12 @@ static int launch_latent_attention(const T* q, long long q_row_stride, const T* 
   else if (dvl_t == 8) BT_LA(2, 8);
   else BT_LA(2, 16);
 #undef BT_LA
+  return 0;
+}
+
+template <typename T>
+static int launch_latent_merge(const float* part, T* out, long long out_row_stride, int n_tokens, int n_heads, int rank,
+                               int n_splits, cudaStream_t stream) {
   if (n_splits > 1) {
     const int n_rows = n_tokens * n_heads;
     BT_PDL_OK("latent_attention_merge",
@@ -381,6 +396,13 @@ extern "C" int bt_head_linear(const void* a, long long a_row_stride, int a_head_
   return fail("head_linear: unknown dtype %d", dtype);
 }
 
+// Rows, (token, head) pairs, that one block of the attention kernel holds for this shape and element type.
+extern "C" int bt_latent_attention_rows(int rank, int rot, int dtype, int tensor_cores) {
+  using namespace bt;
+  if (dtype == kBF16 && tensor_cores && latent_attention_mma_supports(rank, rot)) return latent_attention_mma_rows();
+  return LA_WARPS * ((rank + 31) / 32 <= 4 ? 4 : 2);
+}
+
 extern "C" long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank, int n_splits) {
   return n_splits > 1 ? (long long)n_tokens * n_heads * n_splits * (rank + 2) : 0;
 }
@@ -389,7 +411,7 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
                                    int table_stride, int table_len, int page_size, const int* seq_start,
                                    const int* past_len, const float* sink, void* out, long long out_row_stride,
                                    float* part, int n_tokens, int n_seqs, int max_new, int n_heads, int rank, int rot,
-                                   float scale, int n_splits, int dtype, cudaStream_t stream) {
+                                   float scale, int n_splits, int tensor_cores, int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && rank > 0 && rot >= 0 && rank <= 512, "latent_attention: bad sizes heads=%d rank=%d rot=%d (rank "
            "at most 512)", n_heads, rank, rot);
@@ -398,14 +420,28 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
   BT_CHECK(table_len > 0 && page_size > 0 && n_seqs <= 65535, "latent_attention: bad table_len %d, page_size %d or %d "
            "sequences", table_len, page_size, n_seqs);
   if (n_tokens == 0 || n_seqs == 0) return 0;
-  if (dtype == kF32)
-    return launch_latent_attention<float>((const float*)q, q_row_stride, (const float*)pool, table, table_stride,
-                                          table_len, page_size, seq_start, past_len, sink, (float*)out, out_row_stride,
-                                          part, n_tokens, n_seqs, max_new, n_heads, rank, rot, scale, n_splits, stream);
-  if (dtype == kBF16)
-    return launch_latent_attention<__nv_bfloat16>((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool,
-                                                  table, table_stride, table_len, page_size, seq_start, past_len, sink,
-                                                  (__nv_bfloat16*)out, out_row_stride, part, n_tokens, n_seqs, max_new,
-                                                  n_heads, rank, rot, scale, n_splits, stream);
+  if (dtype == kF32) {
+    if (int e = launch_latent_attention<float>((const float*)q, q_row_stride, (const float*)pool, table, table_stride,
+                                               table_len, page_size, seq_start, past_len, sink, (float*)out,
+                                               out_row_stride, part, n_tokens, n_seqs, max_new, n_heads, rank, rot, scale,
+                                               n_splits, stream))
+      return e;
+    return launch_latent_merge<float>(part, (float*)out, out_row_stride, n_tokens, n_heads, rank, n_splits, stream);
+  }
+  if (dtype == kBF16) {
+    int e;
+    if (tensor_cores && latent_attention_mma_supports(rank, rot))
+      e = launch_latent_attention_mma((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool, table,
+                                      table_stride, table_len, page_size, seq_start, past_len, sink, (__nv_bfloat16*)out,
+                                      out_row_stride, part, n_seqs, max_new, n_heads, rank, rot, scale, n_splits, stream);
+    else
+      e = launch_latent_attention<__nv_bfloat16>((const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)pool, table,
+                                                 table_stride, table_len, page_size, seq_start, past_len, sink,
+                                                 (__nv_bfloat16*)out, out_row_stride, part, n_tokens, n_seqs, max_new,
+                                                 n_heads, rank, rot, scale, n_splits, stream);
+    if (e) return e;
+    return launch_latent_merge<__nv_bfloat16>(part, (__nv_bfloat16*)out, out_row_stride, n_tokens, n_heads, rank,
+                                              n_splits, stream);
+  }
   return fail("latent_attention: unknown dtype %d", dtype);
 }

@@ -50,9 +50,11 @@ class KernelProfile:
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
             "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats")
 
-    def __init__(self):
+    def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
         self.pending = (0.0, 0.0)
+        # the length of the profiled sequences, for kernels whose work depends on lengths that only the device knows
+        self.context_hint = context_hint
 
     def __enter__(self):
         global _PROFILE
@@ -696,14 +698,22 @@ def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:
     return int(library().bt_latent_attention_scratch_floats(c_int(n_tokens), c_int(n_heads), c_int(rank), c_int(n_splits)))
 
 
+def latent_attention_rows(rank, rot, dtype, tensor_cores=True) -> int:
+    """Rows, (token, head) pairs, one block of the attention kernel holds for this shape."""
+    return \
+        int(library().bt_latent_attention_rows(c_int(rank), c_int(rot), c_int(_code(dtype)), c_int(1 if tensor_cores else 0)))
+
+
 def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_tokens, n_seqs, max_new, n_heads, rank,
-                     rot, scale, sink=None, n_splits=1, scratch=None):
+                     rot, scale, sink=None, n_splits=1, scratch=None, tensor_cores=True):
     """Causal attention of the step's tokens over their sequences' latent pages.
 
     q: [tokens, heads * (rank + rot)] (per head: the query carried into the latent space, then its rotated part);
     pool: [pages, PAGE_SIZE, rank + rot]; out: [tokens, heads * rank] = softmax-weighted sums of the latent rows.
     `sink` [heads] (32-bit) adds exp(sink_h) to head h's denominator.  With `n_splits` > 1 the keys of a row tile are
-    cut into that many runs whose partial results meet in `scratch` (32-bit, latent_attention_scratch_floats)."""
+    cut into that many runs whose partial results meet in `scratch` (32-bit, latent_attention_scratch_floats).
+    bfloat16 runs on tensor cores where the shape allows it (rank + rot a multiple of 8, rank a multiple of 8, 16 or 32
+    up to 128, 256, 512); `tensor_cores=False` keeps it on the 32-bit multiply-add kernel that every other case takes."""
     dk = rank + rot
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * dk))
     _need(out, "out", q.dtype, (None, n_heads * rank))
@@ -717,11 +727,19 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
         need = latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise ShapeError(f"latent_attention: {n_splits} splits need {need} floats of scratch")
+    if _PROFILE is not None:
+        # (a rough count for a profile: every row sees half of `ctx` keys in a prompt, all of them in a decode step; the
+        # cache rows of a sequence move once per row tile)
+        ctx = float(_PROFILE.context_hint or 0)
+        seen = ctx if max_new == 1 else ctx / 2
+        _work(2.0 * n_tokens * n_heads * seen * (dk + rank), n_seqs * ctx * dk * q.element_size()
+              + n_tokens * n_heads * (dk + rank) * q.element_size())
     _check(library().bt_latent_attention(
         _ptr(q), c_longlong(q.shape[1]), _ptr(pool), _ptr(table), c_int(table.shape[1]), c_int(table_len),
         c_int(PAGE_SIZE), _ptr(seq_start), _ptr(past_len), _ptr(sink), _ptr(out), c_longlong(out.shape[1]),
         _ptr(scratch if n_splits > 1 else None), c_int(n_tokens), c_int(n_seqs), c_int(max_new), c_int(n_heads),
-        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(_code(q.dtype)), _stream()))
+        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(1 if tensor_cores else 0), c_int(_code(q.dtype)),
+        _stream()))
 
 
 def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, out, *, n_seqs, n_heads, dim, vdim):
@@ -734,6 +752,9 @@ def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, ou
     _need(out, "out", torch.float32, (None, n_heads * vdim))
     if max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
         raise ShapeError("lightning_scan: the channel offsets leave the rows of proj")
+    n_rows = out.shape[0]
+    _work(4.0 * n_rows * n_heads * dim * vdim, n_rows * n_heads * ((2 * dim + vdim) * proj.element_size() + 4 * vdim)
+          + 8.0 * n_seqs * n_heads * dim * vdim)
     _check(library().bt_lightning_scan(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
                                        _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay), _ptr(out),
                                        c_longlong(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),

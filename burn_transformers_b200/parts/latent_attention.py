@@ -121,7 +121,7 @@ class LatentAttention(Mixer):
         if rot:
             self.positions.rotate_vectors(ctx, q_heads[:, :, self.dim:], q_latent_heads[:, :, rank:])
         mixed_latent = ctx.ws.take((n, heads * rank), dtype)
-        splits = self._splits(ctx, 32 if rank <= 128 else 16)
+        splits = self._splits(ctx, kernels.latent_attention_rows(rank, rot, dtype))
         scratch = None
         if splits > 1:
             scratch = ctx.ws.take((kernels.latent_attention_scratch_floats(n, heads, rank, splits),), torch.float32)

@@ -110,10 +110,16 @@ def latent_reference(q, rows, rank, scale, sink, past, seq_of, pos_of):
 
 
 @pytest.mark.parametrize("dtype, tol", DTYPES)
-@pytest.mark.parametrize("heads, rank, rot, splits", [(3, 24, 6, 1), (5, 72, 0, 3), (40, 160, 8, 1), (2, 300, 4, 7)])
-def test_latent_attention_over_scattered_pages(dtype, tol, heads, rank, rot, splits):
+@pytest.mark.parametrize("heads, rank, rot, splits", [(3, 24, 6, 1), (5, 72, 0, 3), (40, 160, 8, 1), (2, 300, 4, 7),
+                                                      (8, 32, 8, 2), (4, 64, 16, 1), (12, 256, 32, 1), (70, 128, 8, 2),
+                                                      (16, 512, 64, 3)])
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_latent_attention_over_scattered_pages(dtype, tol, heads, rank, rot, splits, tensor_cores):
     """Prompts that continue cached sequences and sequences of one new token, with and without a sink, any number of
-    splits: every row against the plain softmax."""
+    splits: every row against the plain softmax.  bfloat16 runs both of its kernels (tensor cores where the shape is
+    one of theirs, and the multiply-add kernel)."""
+    if dtype == torch.float32 and not tensor_cores:
+        pytest.skip("32-bit has one kernel")
     rng = np.random.default_rng(rank)
     dk = rank + rot
     lengths, new = [130, 64, 33, 1], [66, 1, 33, 1]          # the sequences' lengths after the step; their new tokens
@@ -136,7 +142,8 @@ def test_latent_attention_over_scattered_pages(dtype, tol, heads, rank, rot, spl
         kernels.latent_attention(q, out, pool, torch.tensor(table, device=DEV), table.shape[1],
                                  torch.tensor(seq_start, device=DEV), torch.tensor(past, device=DEV), n_tokens=n,
                                  n_seqs=len(new), max_new=max(new), n_heads=heads, rank=rank, rot=rot, scale=0.21,
-                                 sink=dev(sink) if use_sink else None, n_splits=splits, scratch=scratch)
+                                 sink=dev(sink) if use_sink else None, n_splits=splits, scratch=scratch,
+                                 tensor_cores=tensor_cores)
         want = latent_reference(host(q).reshape(n, heads, dk), rows, rank, 0.21, sink if use_sink else None, past, seq_of,
                                 pos_of)
         assert rel(host(out[:n]).reshape(n, heads, rank), want) < tol
@@ -145,7 +152,8 @@ def test_latent_attention_over_scattered_pages(dtype, tol, heads, rank, rot, spl
 
 @pytest.mark.parametrize("target", [0, 31, 32, 63, 64, 65, 500, 699])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_one_key_among_hundreds_carries_the_row(target, splits):
+@pytest.mark.parametrize("dtype, close", [(torch.float32, 1e-3), (torch.bfloat16, 2e-2)])
+def test_one_key_among_hundreds_carries_the_row(target, splits, dtype, close):
     """A query that matches one far key and nothing else must return that key's latent: a key that is skipped, read from
     a wrong page or masked by mistake shows at once.  The same key planted one position AFTER the query must stay
     unseen."""
@@ -157,34 +165,34 @@ def test_one_key_among_hundreds_carries_the_row(target, splits):
     rows[target, rank:] = 3.0                       # loud in the shared rotated part
     rows[target, :rank] = np.linspace(-1, 1, rank)
     table, n_pages = pages_for([length], rng)
-    pool = torch.zeros((n_pages, 64, dk), device=DEV)
+    pool = torch.zeros((n_pages, 64, dk), dtype=dtype, device=DEV)
     for p in range(length):
-        pool[table[0, p // 64], p % 64] = dev(rows[p])
+        pool[table[0, p // 64], p % 64] = dev(rows[p], dtype)
     q = np.zeros((2, heads, dk))
     q[:, :, rank:] = 3.0
     # two query tokens in one step: one right before the target (must not see it), the last one of the sequence
     first_pos = max(0, target - 1)
-    out = torch.zeros((2, heads * rank), device=DEV)
+    out = torch.zeros((2, heads * rank), dtype=dtype, device=DEV)
     scratch = torch.zeros(max(1, kernels.latent_attention_scratch_floats(2, heads, rank, splits)), device=DEV)
     for pos in (first_pos, length - 1):
-        kernels.latent_attention(dev(q.reshape(2, heads * dk)), out, pool, torch.tensor(table, device=DEV), table.shape[1],
+        kernels.latent_attention(dev(q.reshape(2, heads * dk), dtype), out, pool, torch.tensor(table, device=DEV), table.shape[1],
                                  torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                                  torch.tensor([pos], dtype=torch.int32, device=DEV), n_tokens=1, n_seqs=1, max_new=1,
                                  n_heads=heads, rank=rank, rot=rot, scale=1.0, sink=None, n_splits=splits, scratch=scratch)
         got = host(out[0]).reshape(heads, rank)
         sees = pos >= target
         if sees:
-            assert np.abs(got - rows[target, :rank]).max() < 1e-3, (pos, target)
+            assert np.abs(got - rows[target, :rank]).max() < close, (pos, target)
         else:
             assert np.abs(got).max() < 0.2, (pos, target)          # only quiet keys: nothing near the planted latent
     # a sink far above every score takes all the weight: the output vanishes
-    kernels.latent_attention(dev(q.reshape(2, heads * dk)), out, pool, torch.tensor(table, device=DEV), table.shape[1],
+    kernels.latent_attention(dev(q.reshape(2, heads * dk), dtype), out, pool, torch.tensor(table, device=DEV), table.shape[1],
                              torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                              torch.tensor([length - 1], dtype=torch.int32, device=DEV), n_tokens=1, n_seqs=1, max_new=1,
                              n_heads=heads, rank=rank, rot=rot, scale=1.0, sink=dev([200.0, -200.0]), n_splits=splits,
                              scratch=scratch)
     got = host(out[0]).reshape(heads, rank)
-    assert np.abs(got[0]).max() < 1e-6 and np.abs(got[1] - rows[target, :rank]).max() < 1e-3
+    assert np.abs(got[0]).max() < 1e-6 and np.abs(got[1] - rows[target, :rank]).max() < close
 
 
 @pytest.mark.parametrize("dtype, tol", DTYPES)
