@@ -90,7 +90,8 @@ int bt_latent_append(const void* src, long long row_stride, const float* norm_we
                      cudaStream_t stream);
 int bt_head_linear(const void* a, long long a_row_stride, int a_head_stride, const void* w, void* out,
                    long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
-                   int gate_head_stride, int n_tokens, int n_heads, int K, int N, int dtype, cudaStream_t stream);
+                   int gate_head_stride, int n_tokens, int n_heads, int K, int N, int tensor_cores, int dtype,
+                   cudaStream_t stream);
 long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank, int n_splits);
 int bt_latent_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
                         int table_len, int page_size, const int* seq_start, const int* past_len, const float* sink,

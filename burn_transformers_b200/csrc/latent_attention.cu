@@ -30,6 +30,15 @@ int launch_latent_attention_mma(const __nv_bfloat16* q, long long q_row_stride, 
                                 int max_new, int n_heads, int rank, int rot, float scale, int n_splits,
                                 cudaStream_t stream);
 
+// per-head products on tensor cores for bfloat16 (head_linear_mma.cu)
+bool head_linear_mma_supports(const void* a, long long a_row_stride, int a_head_stride, const void* w, const void* out,
+                              long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
+                              int gate_head_stride, int K, int N);
+int launch_head_linear_mma(const __nv_bfloat16* a, long long a_row_stride, int a_head_stride, const __nv_bfloat16* w,
+                           __nv_bfloat16* out, long long out_row_stride, int out_head_stride, const __nv_bfloat16* gate,
+                           long long gate_row_stride, int gate_head_stride, int n_tokens, int n_heads, int K, int N,
+                           cudaStream_t stream);
+
 // ---- filing the latent ------------------------------------------------------------------------------------------
 
 // One block per new token.  src row: [rank latent channels | rot key channels] at `src + t * row_stride`.
@@ -254,34 +263,50 @@ latent_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
   }
 }
 
-// One warp per (token, head): joins the splits' partials in split order.
+// One warp per (token, head): joins the splits' partials.  The lanes first turn the splits' maxima and denominators into
+// one weight per split (shared memory), then every lane sums its channels over the splits, in split order.
+constexpr int LA_MAX_SPLITS = 64;
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ part, T* __restrict__ out, long long out_row_stride, int n_rows,
                               int n_heads, int rank, int n_splits) {
+  __shared__ float weight[4][LA_MAX_SPLITS];
   pdl_trigger();
   pdl_wait();
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + wid;
   if (row >= n_rows) return;
   const float* src = part + (long long)row * n_splits * (rank + 2);
+  float m[LA_MAX_SPLITS / 32], l[LA_MAX_SPLITS / 32];
   float top = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) top = fmaxf(top, src[s * (rank + 2) + rank]);
-  float denom = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = src[s * (rank + 2) + rank];
-    if (m != -INFINITY) denom += src[s * (rank + 2) + rank + 1] * expf(m - top);
+#pragma unroll
+  for (int i = 0; i < LA_MAX_SPLITS / 32; ++i) {
+    const int s = lane + 32 * i;
+    m[i] = s < n_splits ? src[(long long)s * (rank + 2) + rank] : -INFINITY;
+    l[i] = s < n_splits ? src[(long long)s * (rank + 2) + rank + 1] : 0.f;
+    top = fmaxf(top, m[i]);
   }
+  top = warp_max(top);
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < LA_MAX_SPLITS / 32; ++i) {
+    m[i] = m[i] == -INFINITY ? 0.f : expf(m[i] - top);
+    denom += l[i] * m[i];
+  }
+  denom = warp_sum(denom);
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
+#pragma unroll
+  for (int i = 0; i < LA_MAX_SPLITS / 32; ++i)
+    if (lane + 32 * i < n_splits) weight[wid][lane + 32 * i] = m[i] * inv;
+  __syncwarp();
   const long long token = row / n_heads;
   const int head = row - (int)token * n_heads;
   for (int c = lane; c < rank; c += 32) {
     float v = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = src[s * (rank + 2) + rank];
-      if (m != -INFINITY) v += src[s * (rank + 2) + c] * expf(m - top);
-    }
-    out[token * out_row_stride + (long long)head * rank + c] = from_float<T>(v * inv);
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) v = fmaf(src[(long long)s * (rank + 2) + c], weight[wid][s], v);
+    out[token * out_row_stride + (long long)head * rank + c] = from_float<T>(v);
   }
 }
 
@@ -379,11 +404,17 @@ extern "C" int bt_latent_append(const void* src, long long row_stride, const flo
 
 extern "C" int bt_head_linear(const void* a, long long a_row_stride, int a_head_stride, const void* w, void* out,
                               long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
-                              int gate_head_stride, int n_tokens, int n_heads, int K, int N, int dtype,
-                              cudaStream_t stream) {
+                              int gate_head_stride, int n_tokens, int n_heads, int K, int N, int tensor_cores,
+                              int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && K > 0 && N > 0, "head_linear: bad sizes heads=%d K=%d N=%d", n_heads, K, N);
   if (n_tokens == 0) return 0;
+  if (dtype == kBF16 && tensor_cores &&
+      head_linear_mma_supports(a, a_row_stride, a_head_stride, w, out, out_row_stride, out_head_stride, gate,
+                               gate_row_stride, gate_head_stride, K, N))
+    return launch_head_linear_mma((const __nv_bfloat16*)a, a_row_stride, a_head_stride, (const __nv_bfloat16*)w,
+                                  (__nv_bfloat16*)out, out_row_stride, out_head_stride, (const __nv_bfloat16*)gate,
+                                  gate_row_stride, gate_head_stride, n_tokens, n_heads, K, N, stream);
   if (dtype == kF32)
     return launch_head_linear<float>((const float*)a, a_row_stride, a_head_stride, (const float*)w, (float*)out,
                                      out_row_stride, out_head_stride, (const float*)gate, gate_row_stride,
@@ -415,7 +446,7 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
   using namespace bt;
   BT_CHECK(n_heads > 0 && rank > 0 && rot >= 0 && rank <= 512, "latent_attention: bad sizes heads=%d rank=%d rot=%d (rank "
            "at most 512)", n_heads, rank, rot);
-  BT_CHECK(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || part != nullptr),
+  BT_CHECK(n_splits >= 1 && n_splits <= LA_MAX_SPLITS && (n_splits == 1 || part != nullptr),
            "latent_attention: %d splits need scratch for their partial results", n_splits);
   BT_CHECK(table_len > 0 && page_size > 0 && n_seqs <= 65535, "latent_attention: bad table_len %d, page_size %d or %d "
            "sequences", table_len, page_size, n_seqs);

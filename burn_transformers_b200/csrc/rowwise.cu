@@ -71,6 +71,32 @@ gated_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long 
   }
 }
 
+// The same for bfloat16 rows whose halves are whole 16-byte pieces: a thread takes 8 channels at a time.
+__global__ void __launch_bounds__(256)
+gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, long long n_rows,
+                               int inner, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int pieces = inner / 8;
+  const long long total = n_rows * pieces;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / pieces;
+    const int j = (int)(i - r * pieces) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(x + r * 2 * inner + j);
+    const uint4 uv = *reinterpret_cast<const uint4*>(x + r * 2 * inner + inner + j);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+      o2[e] = __floats2bfloat162_rn(apply_activation(g.x, act) * u.x, apply_activation(g.y, act) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + r * inner + j) = ov;
+  }
+}
+
 __global__ void __launch_bounds__(256) scale_kernel(float* __restrict__ x, long long n, float scale) {
   pdl_trigger();
   pdl_wait();
@@ -147,7 +173,12 @@ extern "C" int bt_gated_activation(const void* x, void* out, long long n_rows, i
   if (dtype == kF32)
     BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1,
                                              (const float*)x, (float*)out, n_rows, inner, act));
-  else if (dtype == kBF16)
+  else if (dtype == kBF16 && inner % 8 == 0 && (unsigned long long)x % 16 == 0 && (unsigned long long)out % 16 == 0) {
+    const long long pieces = total / 8;
+    const int b8 = (int)((pieces + 255) / 256 < 148 * 16 ? (pieces + 255) / 256 : 148 * 16);
+    BT_PDL_OK("gated_activation", launch_pdl(gated_activation_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, 1,
+                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act));
+  } else if (dtype == kBF16)
     BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1,
                                              (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act));
   else

@@ -48,7 +48,8 @@ class KernelProfile:
     CUDA graph cannot be timed this way: profile steps that run their kernels directly."""
 
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
-            "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats")
+            "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats",
+            "bt_latent_attention_rows")
 
     def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
@@ -672,10 +673,11 @@ def _head_view(t, name, n_heads, width):
     return t.stride(0), t.stride(1)
 
 
-def head_linear(a, w, out, *, n_tokens, gate=None):
+def head_linear(a, w, out, *, n_tokens, gate=None, tensor_cores=True):
     """out[t, h, :] = a[t, h, :] @ w[h]  (times sigmoid(gate[t, h, :]) if `gate`), sums in 32-bit.
 
-    a: view [tokens, heads, K]; w: [heads, K, N] contiguous; out and gate: views [tokens, heads, N]."""
+    a: view [tokens, heads, K]; w: [heads, K, N] contiguous; out and gate: views [tokens, heads, N].  bfloat16 operands
+    that lie on 16-byte boundaries with K and N multiples of 8 run on tensor cores (`tensor_cores=False`: never)."""
     n_heads, k, n = w.shape
     _need(w, "w", (torch.float32, torch.bfloat16), (n_heads, k, n))
     a_rs, a_hs = _head_view(a, "a", n_heads, k)
@@ -691,7 +693,8 @@ def head_linear(a, w, out, *, n_tokens, gate=None):
     _work(2.0 * n_tokens * n_heads * k * n, (n_tokens * n_heads * (k + n) + n_heads * k * n) * w.element_size())
     _check(library().bt_head_linear(_ptr(a), c_longlong(a_rs), c_int(a_hs), _ptr(w), _ptr(out), c_longlong(o_rs),
                                     c_int(o_hs), _ptr(gate), c_longlong(g_rs), c_int(g_hs), c_int(n_tokens),
-                                    c_int(n_heads), c_int(k), c_int(n), c_int(_code(w.dtype)), _stream()))
+                                    c_int(n_heads), c_int(k), c_int(n), c_int(1 if tensor_cores else 0),
+                                    c_int(_code(w.dtype)), _stream()))
 
 
 def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:

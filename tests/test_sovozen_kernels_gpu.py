@@ -59,9 +59,10 @@ def test_rms_norm_with_and_without_a_gate(dtype, tol, gated):
 
 
 @pytest.mark.parametrize("dtype, tol", DTYPES)
-def test_gated_activation(dtype, tol):
+@pytest.mark.parametrize("inner", [50, 64, 200])
+def test_gated_activation(dtype, tol, inner):
     rng = np.random.default_rng(2)
-    n, inner = 6, 50
+    n = 6
     x = dev(rng.standard_normal((n, 2 * inner)) * 2.0, dtype)
     out = torch.zeros((n + 1, inner), dtype=dtype, device=DEV)
     kernels.gated_activation(x, out, n_rows=n, activation="gelu_new")
@@ -70,11 +71,13 @@ def test_gated_activation(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype, tol", DTYPES)
-def test_products_per_head_with_a_gate(dtype, tol):
+@pytest.mark.parametrize("n, heads, k, width, skip", [(19, 3, 21, 13, 4), (70, 3, 64, 72, 8), (5, 2, 256, 64, 0),
+                                                      (130, 5, 40, 24, 16), (64, 1, 72, 136, 8)])
+def test_products_per_head_with_a_gate(dtype, tol, n, heads, k, width, skip):
+    """Odd sizes take the multiply-add kernel; in bfloat16, operands on 16-byte boundaries take the tensor cores."""
     rng = np.random.default_rng(3)
-    n, heads, k, width = 19, 3, 21, 13
-    a_rows = dev(rng.standard_normal((n, heads * (k + 4))), dtype)
-    a = a_rows.view(n, heads, k + 4)[:, :, 4:]
+    a_rows = dev(rng.standard_normal((n, heads * (k + skip))), dtype)
+    a = a_rows.view(n, heads, k + skip)[:, :, skip:]
     w = dev(rng.standard_normal((heads, k, width)) / np.sqrt(k), dtype)
     gate = dev(rng.standard_normal((n, heads, width)), dtype)
     out = torch.zeros((n + 1, heads, width), dtype=dtype, device=DEV)
