@@ -102,6 +102,11 @@ int bt_latent_attention_rows(int rank, int rot, int dtype, int tensor_cores);
 int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                       const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
                       int n_seqs, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream);
+long long bt_lightning_chunked_scratch_floats(int n_seqs, int max_new, int n_heads, int dim, int vdim);
+int bt_lightning_chunked(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
+                         const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,
+                         float* scratch, int max_new, int n_seqs, int n_heads, int dim, int vdim, int dtype,
+                         cudaStream_t stream);
 int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate, int gate_dtype,
                long long gate_row_stride, void* out, int out_dtype, long long out_row_stride, int n_rows, int width,
                float eps, cudaStream_t stream);

@@ -123,3 +123,221 @@ extern "C" int bt_lightning_scan(const void* proj, long long row_stride, int q_o
                                            seq_start, decay, out, out_row_stride, n_seqs, n_heads, dim, vdim, stream);
   return fail("lightning_scan: unknown dtype %d", dtype);
 }
+
+// ---- long runs of new tokens: the same recurrence by chunks ------------------------------------------------------
+//
+// Unrolled over a chunk of C tokens that starts from the state S_in, the recurrence reads
+//
+//     o_t   = decay^(t+1) S_in^T q_t + sum_{s <= t} decay^(t-s) (q_t . k_s) v_s          (t, s count inside the chunk)
+//     S_out = decay^C S_in + sum_s decay^(C-1-s) k_s v_s^T
+//
+// so the chunks of a long prompt work side by side: lightning_chunk_kernel forms, per chunk, the sums over s (the part
+// of o_t that needs no earlier chunk, and the chunk's own contribution to the state); lightning_prefix_kernel walks the
+// chunks of a sequence in order, turning each contribution into the state its chunk starts from; lightning_carry_kernel
+// adds decay^(t+1) S_in^T q_t.  Everything is 32-bit multiply-adds; powers of the decay come from powf.
+namespace bt {
+
+constexpr int LC = 64;   // tokens per chunk
+
+// grid (chunks, heads * column blocks, sequences); 256 threads; a block owns `cols` (<= 64) value channels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_off, int k_off, int v_off,
+                       const int* __restrict__ seq_start, const float* __restrict__ decay, float* __restrict__ out,
+                       long long out_row_stride, float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim,
+                       int cols, int col_blocks) {
+  extern __shared__ float sm[];
+  const int ldk = dim + 1;
+  float* q_s = sm;                       // [LC][ldk]
+  float* k_s = q_s + LC * ldk;           // [LC][ldk]
+  float* v_s = k_s + LC * ldk;           // [LC][cols]
+  float* a_s = v_s + LC * cols;          // [LC][LC + 1]
+  float* pw = a_s + LC * (LC + 1);       // [LC + 1] powers of the decay
+  pdl_trigger();
+  pdl_wait();
+  const int chunk = blockIdx.x, seq = blockIdx.z;
+  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * cols;
+  const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
+  if (chunk * LC >= n_new) return;
+  const int len = min(LC, n_new - chunk * LC);
+  const long long row0 = first + (long long)chunk * LC;
+  const float lam = decay[head];
+  const int tid = threadIdx.x;
+  for (int i = tid; i <= LC; i += 256) pw[i] = powf(lam, (float)i);
+  for (int i = tid; i < LC * dim; i += 256) {
+    const int t = i / dim, d = i - t * dim;
+    float qv = 0.f, kv = 0.f;
+    if (t < len) {
+      const T* row = proj + (row0 + t) * row_stride + (long long)head * dim + d;
+      qv = silu(to_float(row[q_off]));
+      kv = silu(to_float(row[k_off]));
+    }
+    q_s[t * ldk + d] = qv;
+    k_s[t * ldk + d] = kv;
+  }
+  for (int i = tid; i < LC * cols; i += 256) {
+    const int t = i / cols, c = i - t * cols;
+    v_s[i] = (t < len && col0 + c < vdim)
+                 ? silu(to_float(proj[(row0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c])) : 0.f;
+  }
+  __syncthreads();
+  // a[t][s] = decay^(t-s) (q_t . k_s) for s <= t
+  for (int i = tid; i < LC * LC; i += 256) {
+    const int t = i / LC, s = i - t * LC;
+    float dot = 0.f;
+    if (s <= t && t < len) {
+      const float* qt = q_s + t * ldk;
+      const float* kr = k_s + s * ldk;
+      for (int d = 0; d < dim; ++d) dot = fmaf(qt[d], kr[d], dot);
+      dot *= pw[t - s];
+    }
+    a_s[t * (LC + 1) + s] = dot;
+  }
+  __syncthreads();
+  // thread = (row group, column): 256 / cols row groups, each with LC / groups tokens
+  const int groups = 256 / cols, gr = tid / cols, c = tid - gr * cols;
+  if (gr < groups && col0 + c < vdim) {
+    // the part of o_t that needs no earlier chunk
+    for (int t = gr; t < len; t += groups) {
+      float o = 0.f;
+      const float* at = a_s + t * (LC + 1);
+      for (int s = 0; s <= t; ++s) o = fmaf(at[s], v_s[s * cols + c], o);
+      out[(row0 + t) * out_row_stride + (long long)head * vdim + col0 + c] = o;
+    }
+    // the chunk's contribution to the state: sum_s decay^(len-1-s) k_s[i] v_s[c]
+    float* dst = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim + col0 + c;
+    for (int i0 = gr; i0 < dim; i0 += groups) {
+      float kv = 0.f;
+      for (int s = 0; s < len; ++s) kv = fmaf(pw[len - 1 - s] * k_s[s * ldk + i0], v_s[s * cols + c], kv);
+      dst[(long long)i0 * vdim] = kv;
+    }
+  }
+}
+
+// One thread per (sequence, head, state element): walks the sequence's chunks in order; leaves in scratch[chunk] the
+// state that chunk STARTS from and in `state` the state after the last one.
+__global__ void __launch_bounds__(256)
+lightning_prefix_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ slots,
+                        const int* __restrict__ seq_start, const float* __restrict__ decay, int max_chunks, int n_heads,
+                        int dim, int vdim) {
+  pdl_trigger();
+  pdl_wait();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int e = blockIdx.x * 256 + threadIdx.x;
+  if (e >= dim * vdim) return;
+  const int n_new = seq_start[seq + 1] - seq_start[seq];
+  const int n_chunks = (n_new + LC - 1) / LC;
+  const float lam = decay[head];
+  const float full = powf(lam, (float)LC);
+  float* st = state + (((long long)slots[seq] * n_heads + head) * dim) * vdim + e;
+  float s = *st;
+  for (int c = 0; c < n_chunks; ++c) {
+    float* cell = scratch + ((((long long)seq * max_chunks + c) * n_heads + head) * dim) * vdim + e;
+    const float kv = *cell;
+    *cell = s;
+    const int len = min(LC, n_new - c * LC);
+    s = fmaf(len == LC ? full : powf(lam, (float)len), s, kv);
+  }
+  *st = s;
+}
+
+// out[t] += decay^(t+1) S_in^T q_t for the tokens of a chunk; grid and blocks as lightning_chunk_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lightning_carry_kernel(const T* __restrict__ proj, long long row_stride, int q_off, const int* __restrict__ seq_start,
+                       const float* __restrict__ decay, float* __restrict__ out, long long out_row_stride,
+                       const float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim, int cols,
+                       int col_blocks) {
+  extern __shared__ float sm[];
+  const int ldk = dim + 1;
+  float* q_s = sm;                 // [LC][ldk], already scaled by decay^(t+1)
+  float* s_s = q_s + LC * ldk;     // [dim][cols]
+  pdl_trigger();
+  pdl_wait();
+  const int chunk = blockIdx.x, seq = blockIdx.z;
+  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * cols;
+  const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
+  if (chunk * LC >= n_new) return;
+  const int len = min(LC, n_new - chunk * LC);
+  const long long row0 = first + (long long)chunk * LC;
+  const float lam = decay[head];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < LC * dim; i += 256) {
+    const int t = i / dim, d = i - t * dim;
+    q_s[t * ldk + d] = t < len ? silu(to_float(proj[(row0 + t) * row_stride + q_off + (long long)head * dim + d])) *
+                                     powf(lam, (float)(t + 1)) : 0.f;
+  }
+  const float* src = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim + col0;
+  for (int i = tid; i < dim * cols; i += 256) {
+    const int d = i / cols, c = i - d * cols;
+    s_s[i] = col0 + c < vdim ? src[(long long)d * vdim + c] : 0.f;
+  }
+  __syncthreads();
+  const int groups = 256 / cols, gr = tid / cols, c = tid - gr * cols;
+  if (gr >= groups || col0 + c >= vdim) return;
+  for (int t = gr; t < len; t += groups) {
+    float o = 0.f;
+    const float* qt = q_s + t * ldk;
+    for (int d = 0; d < dim; ++d) o = fmaf(qt[d], s_s[d * cols + c], o);
+    out[(row0 + t) * out_row_stride + (long long)head * vdim + col0 + c] += o;
+  }
+}
+
+template <typename T>
+static int launch_lightning_chunked(const T* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
+                                    const int* slots, const int* seq_start, const float* decay, float* out,
+                                    long long out_row_stride, float* scratch, int max_new, int n_seqs, int n_heads, int dim,
+                                    int vdim, cudaStream_t stream) {
+  const int cols = vdim < 64 ? (vdim <= 32 ? 32 : 64) : 64;
+  const int col_blocks = (vdim + cols - 1) / cols;
+  const int max_chunks = (max_new + LC - 1) / LC;
+  BT_CHECK((long long)n_heads * col_blocks <= 65535, "lightning_scan: %d heads x %d column blocks are too many", n_heads, col_blocks);
+  const dim3 grid(max_chunks, n_heads * col_blocks, n_seqs), block(256);
+  const size_t smem_a = ((size_t)2 * LC * (dim + 1) + (size_t)LC * cols + (size_t)LC * (LC + 1) + LC + 1) * sizeof(float);
+  const size_t smem_c = ((size_t)LC * (dim + 1) + (size_t)dim * cols) * sizeof(float);
+  auto chunk_kernel = lightning_chunk_kernel<T>;
+  auto carry_kernel = lightning_carry_kernel<T>;
+  if (smem_a > 48 * 1024)
+    BT_CHECK(cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a) == cudaSuccess,
+             "lightning_scan: cannot reserve %zu bytes of shared memory", smem_a);
+  if (smem_c > 48 * 1024)
+    BT_CHECK(cudaFuncSetAttribute(carry_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c) == cudaSuccess,
+             "lightning_scan: cannot reserve %zu bytes of shared memory", smem_c);
+  BT_PDL_OK("lightning_chunk", launch_pdl(chunk_kernel, grid, block, smem_a, stream, 1, proj, row_stride, q_off, k_off, v_off,
+                                          seq_start, decay, out, out_row_stride, scratch, max_chunks, n_heads, dim, vdim,
+                                          cols, col_blocks));
+  BT_PDL_OK("lightning_prefix", launch_pdl(lightning_prefix_kernel, dim3((dim * vdim + 255) / 256, n_heads, n_seqs), block, 0,
+                                           stream, 1, scratch, state, slots, seq_start, decay, max_chunks, n_heads, dim,
+                                           vdim));
+  BT_PDL_OK("lightning_carry", launch_pdl(carry_kernel, grid, block, smem_c, stream, 1, proj, row_stride, q_off, seq_start,
+                                          decay, out, out_row_stride, (const float*)scratch, max_chunks, n_heads, dim, vdim,
+                                          cols, col_blocks));
+  return 0;
+}
+
+}  // namespace bt
+
+// Floats of scratch the chunked form needs for runs of up to `max_new` new tokens.
+extern "C" long long bt_lightning_chunked_scratch_floats(int n_seqs, int max_new, int n_heads, int dim, int vdim) {
+  return (long long)n_seqs * ((max_new + bt::LC - 1) / bt::LC) * n_heads * dim * vdim;
+}
+
+// The recurrence for steps that bring long runs of tokens: the same results as bt_lightning_scan (beyond rounding), the
+// chunks of a run worked side by side.  `max_new`: no sequence of the step brings more tokens than this.
+extern "C" int bt_lightning_chunked(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
+                                    const int* slots, const int* seq_start, const float* decay, float* out,
+                                    long long out_row_stride, float* scratch, int max_new, int n_seqs, int n_heads, int dim,
+                                    int vdim, int dtype, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_heads > 0 && dim > 0 && dim <= 256 && vdim > 0 && n_seqs >= 0 && n_seqs <= 65535 && max_new > 0 && scratch,
+           "lightning_chunked: bad sizes seqs=%d heads=%d dim=%d vdim=%d max_new=%d", n_seqs, n_heads, dim, vdim, max_new);
+  if (n_seqs == 0) return 0;
+  if (dtype == kF32)
+    return launch_lightning_chunked<float>((const float*)proj, row_stride, q_off, k_off, v_off, state, slots, seq_start,
+                                           decay, out, out_row_stride, scratch, max_new, n_seqs, n_heads, dim, vdim, stream);
+  if (dtype == kBF16)
+    return launch_lightning_chunked<__nv_bfloat16>((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, state,
+                                                   slots, seq_start, decay, out, out_row_stride, scratch, max_new, n_seqs,
+                                                   n_heads, dim, vdim, stream);
+  return fail("lightning_chunked: unknown dtype %d", dtype);
+}

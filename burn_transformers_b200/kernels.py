@@ -32,6 +32,7 @@ def library() -> ctypes.CDLL:
         lib.bt_last_error.restype = ctypes.c_char_p
         lib.bt_attention_decode_scratch_floats.restype = c_longlong
         lib.bt_latent_attention_scratch_floats.restype = c_longlong
+        lib.bt_lightning_chunked_scratch_floats.restype = c_longlong
         lib.bt_launch_count.restype = c_longlong
         if lib.bt_abi_version() != 1:
             raise KernelError(f"{path} has an unexpected interface version")
@@ -49,7 +50,7 @@ class KernelProfile:
 
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
             "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats",
-            "bt_latent_attention_rows")
+            "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats")
 
     def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
@@ -745,10 +746,22 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
         _stream()))
 
 
-def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, out, *, n_seqs, n_heads, dim, vdim):
+LIGHTNING_CHUNK = 64      # runs of more new tokens than this take the chunked form of the recurrence
+
+
+def lightning_chunked_scratch_floats(n_seqs, max_new, n_heads, dim, vdim) -> int:
+    return int(library().bt_lightning_chunked_scratch_floats(c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(dim),
+                                                             c_int(vdim)))
+
+
+def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, out, *, n_seqs, n_heads, dim, vdim,
+                   max_new=None, scratch=None):
     """Runs S <- decay_h S + k v^T, o = S^T q over the step's tokens of every sequence, with q, k, v = x * sigmoid(x) of
     the channels at `q_off`, `k_off`, `v_off` of the rows of `proj`.  state: [slots, heads, dim, vdim] 32-bit, read and
-    written at the rows `slots[seq]`; out: [tokens, heads * vdim] 32-bit."""
+    written at the rows `slots[seq]`; out: [tokens, heads * vdim] 32-bit.
+
+    With `max_new` (no sequence brings more tokens) above LIGHTNING_CHUNK and `scratch` (32-bit,
+    lightning_chunked_scratch_floats) the chunks of a long run are worked side by side; else token by token."""
     _need(proj, "proj", (torch.float32, torch.bfloat16))
     _need(state, "state", torch.float32, (None, n_heads, dim, vdim))
     _need(decay, "decay", torch.float32, (n_heads,))
@@ -758,6 +771,16 @@ def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, ou
     n_rows = out.shape[0]
     _work(4.0 * n_rows * n_heads * dim * vdim, n_rows * n_heads * ((2 * dim + vdim) * proj.element_size() + 4 * vdim)
           + 8.0 * n_seqs * n_heads * dim * vdim)
+    if max_new is not None and max_new > LIGHTNING_CHUNK and scratch is not None:
+        need = lightning_chunked_scratch_floats(n_seqs, max_new, n_heads, dim, vdim)
+        if scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_cuda:
+            raise ShapeError(f"lightning_scan: runs of {max_new} tokens need {need} floats of scratch")
+        _check(library().bt_lightning_chunked(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off),
+                                              c_int(v_off), _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay),
+                                              _ptr(out), c_longlong(out.shape[1]), _ptr(scratch), c_int(max_new),
+                                              c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
+                                              c_int(_code(proj.dtype)), _stream()))
+        return
     _check(library().bt_lightning_scan(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
                                        _ptr(state), _ptr(slots), _ptr(seq_start), _ptr(decay), _ptr(out),
                                        c_longlong(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),

@@ -63,9 +63,14 @@ class LightningAttention(Mixer):
         proj = ctx.ws.take((n, self.in_width), ctx.dtype)
         linear(ctx, x, self.t_in_weight, None, proj, m=n, w_is_nk=True)
         read = ctx.ws.take((n, self.v_width), torch.float32)
+        scratch = None
+        if ctx.max_new > kernels.LIGHTNING_CHUNK:
+            # long runs of new tokens: the chunks of a run are worked side by side (csrc/lightning.cu)
+            scratch = ctx.ws.take((kernels.lightning_chunked_scratch_floats(ctx.n_seqs, ctx.max_new, self.n_heads, self.dim,
+                                                                            self.vdim),), torch.float32)
         kernels.lightning_scan(proj, 0, self.qk_width, 2 * self.qk_width, ctx.cache.state(entry, "s"), ctx.slots,
                                ctx.seq_start, self.decay_device, read, n_seqs=ctx.n_seqs, n_heads=self.n_heads,
-                               dim=self.dim, vdim=self.vdim)
+                               dim=self.dim, vdim=self.vdim, max_new=ctx.max_new, scratch=scratch)
         mixed = ctx.ws.take((n, self.v_width), ctx.dtype)
         kernels.rmsnorm(read, self.t_norm_weight, mixed, self.eps, n_rows=n, gate=proj[:, 2 * self.qk_width + self.v_width:])
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)

@@ -226,16 +226,17 @@ def test_latent_rows_are_normed_turned_and_filed(dtype, tol):
 
 @pytest.mark.parametrize("dtype, tol", DTYPES)
 @pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 24), (1, 40, 8), (3, 128, 70), (2, 200, 33)])
-def test_recurrence_carries_its_state_from_step_to_step(dtype, tol, heads, dim, vdim):
-    """Three sequences in scattered slots: a prompt, then a portion, then one token each; the state after every step
-    and every output against the plain recurrence over the whole sequences."""
+@pytest.mark.parametrize("steps", [[[40, 1, 17], [2, 33, 1], [1, 1, 1]], [[150, 64, 65], [70, 1, 129], [1, 1, 1]]])
+def test_recurrence_carries_its_state_from_step_to_step(dtype, tol, heads, dim, vdim, steps):
+    """Three sequences in scattered slots: a prompt, then a portion, then one token each; every output against the plain
+    recurrence over the whole sequences.  Runs of more than 64 tokens take the chunked form (whole chunks, a ragged last
+    chunk, a state carried in from the step before); shorter ones go token by token."""
     rng = np.random.default_rng(dim)
     decay = rng.uniform(0.5, 1.0, heads)
     slots = np.asarray([5, 0, 3], dtype=np.int32)
     state = torch.zeros((7, heads, dim, vdim), device=DEV)
     state[1] = 4.0                                              # a slot of another sequence: must stay as it is
     width = 2 * heads * dim + heads * vdim + 5
-    steps = [[40, 1, 17], [2, 33, 1], [1, 1, 1]]
     totals = np.sum(steps, axis=0)
     rows = [np.asarray(host(dev(rng.standard_normal((n, width)), dtype))) for n in totals]
     want = []
@@ -256,9 +257,10 @@ def test_recurrence_carries_its_state_from_step_to_step(dtype, tol, heads, dim, 
         n = sum(step)
         out = torch.zeros((n + 1, heads * vdim), device=DEV)
         seq_start = np.concatenate([[0], np.cumsum(step)]).astype(np.int32)
+        scratch = torch.zeros(max(1, kernels.lightning_chunked_scratch_floats(3, max(step), heads, dim, vdim)), device=DEV)
         kernels.lightning_scan(proj, 3, 3 + heads * dim, 5 + 2 * heads * dim, state, torch.tensor(slots, device=DEV),
                                torch.tensor(seq_start, device=DEV), dev(decay), out, n_seqs=3, n_heads=heads, dim=dim,
-                               vdim=vdim)
+                               vdim=vdim, max_new=max(step), scratch=scratch)
         expect = np.concatenate([want[i][fed[i]:fed[i] + m] for i, m in enumerate(step)])
         assert rel(host(out[:n]), expect) < tol and bool((out[n:] == 0).all())
         fed = [f + m for f, m in zip(fed, step)]
