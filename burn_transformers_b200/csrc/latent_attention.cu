@@ -263,21 +263,24 @@ latent_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
   }
 }
 
-// One warp per (token, head): joins the splits' partials.  The lanes first turn the splits' maxima and denominators into
-// one weight per split (shared memory), then every lane sums its channels over the splits, in split order.
+// Joins the splits' partials.  A warp takes 32 channels of one (token, head): its lanes first turn the splits' maxima
+// and denominators into one weight per split (shared memory), then every lane sums its channel over the splits, in
+// split order.
 constexpr int LA_MAX_SPLITS = 64;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ part, T* __restrict__ out, long long out_row_stride, int n_rows,
-                              int n_heads, int rank, int n_splits) {
+                              int n_heads, int rank, int n_splits, int groups) {
   __shared__ float weight[4][LA_MAX_SPLITS];
   pdl_trigger();
   pdl_wait();
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + wid;
+  const long long unit = (long long)blockIdx.x * 4 + wid;      // (row, group of 32 channels)
+  const long long row = unit / groups;
+  const int c = (int)(unit - row * groups) * 32 + lane;
   if (row >= n_rows) return;
-  const float* src = part + (long long)row * n_splits * (rank + 2);
+  const float* src = part + row * n_splits * (rank + 2);
   float m[LA_MAX_SPLITS / 32], l[LA_MAX_SPLITS / 32];
   float top = -INFINITY;
 #pragma unroll
@@ -300,14 +303,13 @@ latent_attention_merge_kernel(const float* __restrict__ part, T* __restrict__ ou
   for (int i = 0; i < LA_MAX_SPLITS / 32; ++i)
     if (lane + 32 * i < n_splits) weight[wid][lane + 32 * i] = m[i] * inv;
   __syncwarp();
+  if (c >= rank) return;
   const long long token = row / n_heads;
-  const int head = row - (int)token * n_heads;
-  for (int c = lane; c < rank; c += 32) {
-    float v = 0.f;
+  const int head = (int)(row - token * n_heads);
+  float v = 0.f;
 #pragma unroll 8
-    for (int s = 0; s < n_splits; ++s) v = fmaf(src[(long long)s * (rank + 2) + c], weight[wid][s], v);
-    out[token * out_row_stride + (long long)head * rank + c] = from_float<T>(v);
-  }
+  for (int s = 0; s < n_splits; ++s) v = fmaf(src[(long long)s * (rank + 2) + c], weight[wid][s], v);
+  out[token * out_row_stride + (long long)head * rank + c] = from_float<T>(v);
 }
 
 template <typename T>
@@ -355,10 +357,11 @@ template <typename T>
 static int launch_latent_merge(const float* part, T* out, long long out_row_stride, int n_tokens, int n_heads, int rank,
                                int n_splits, cudaStream_t stream) {
   if (n_splits > 1) {
-    const int n_rows = n_tokens * n_heads;
+    const int n_rows = n_tokens * n_heads, groups = (rank + 31) / 32;
+    const long long units = (long long)n_rows * groups;
     BT_PDL_OK("latent_attention_merge",
-              launch_pdl(latent_attention_merge_kernel<T>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, 1,
-                         (const float*)part, out, out_row_stride, n_rows, n_heads, rank, n_splits));
+              launch_pdl(latent_attention_merge_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, 1,
+                         (const float*)part, out, out_row_stride, n_rows, n_heads, rank, n_splits, groups));
   }
   return 0;
 }

@@ -137,32 +137,36 @@ extern "C" int bt_lightning_scan(const void* proj, long long row_stride, int q_o
 // adds decay^(t+1) S_in^T q_t.  Everything is 32-bit multiply-adds; powers of the decay come from powf.
 namespace bt {
 
-constexpr int LC = 64;   // tokens per chunk
+constexpr int LC = 64;    // tokens per chunk
+constexpr int LCP = 68;   // row length of the transposed tiles: 16-byte rows, four-way conflicts at most when they are written
 
-// grid (chunks, heads * column blocks, sequences); 256 threads; a block owns `cols` (<= 64) value channels.
+// Tiles of shared memory hold their 64 tokens along the fast axis ([channel][token], rows of LCP floats), so that a
+// thread reads four tokens, or four value channels, with one 16-byte load and every product phase is 16 multiply-adds
+// per two such loads.  Threads form a 16 x 16 grid; thread (ty, tx) owns a 4 x 4 patch of every product.
+
+// grid (chunks, heads * column blocks, sequences); 256 threads; a block owns 64 value channels.
 template <typename T>
 __global__ void __launch_bounds__(256)
 lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_off, int k_off, int v_off,
                        const int* __restrict__ seq_start, const float* __restrict__ decay, float* __restrict__ out,
                        long long out_row_stride, float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim,
                        int cols, int col_blocks) {
-  extern __shared__ float sm[];
-  const int ldk = dim + 1;
-  float* q_s = sm;                       // [LC][ldk]
-  float* k_s = q_s + LC * ldk;           // [LC][ldk]
-  float* v_s = k_s + LC * ldk;           // [LC][cols]
-  float* a_s = v_s + LC * cols;          // [LC][LC + 1]
-  float* pw = a_s + LC * (LC + 1);       // [LC + 1] powers of the decay
+  extern __shared__ __align__(16) float sm[];
+  float* q_t = sm;                       // [dim][LCP]   q_t[d][t]
+  float* k_t = q_t + dim * LCP;          // [dim][LCP]   k_t[d][s]
+  float* v_s = k_t + dim * LCP;          // [LC][64]     v_s[s][j]
+  float* a_t = v_s + LC * 64;            // [LC][LCP]    a_t[s][t] = decay^(t-s) (q_t . k_s), zero for s > t
+  float* pw = a_t + LC * LCP;            // [LC + 4] powers of the decay
   pdl_trigger();
   pdl_wait();
   const int chunk = blockIdx.x, seq = blockIdx.z;
-  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * cols;
+  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * 64;
   const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
   if (chunk * LC >= n_new) return;
   const int len = min(LC, n_new - chunk * LC);
   const long long row0 = first + (long long)chunk * LC;
   const float lam = decay[head];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   for (int i = tid; i <= LC; i += 256) pw[i] = powf(lam, (float)i);
   for (int i = tid; i < LC * dim; i += 256) {
     const int t = i / dim, d = i - t * dim;
@@ -172,52 +176,109 @@ lightning_chunk_kernel(const T* __restrict__ proj, long long row_stride, int q_o
       qv = silu(to_float(row[q_off]));
       kv = silu(to_float(row[k_off]));
     }
-    q_s[t * ldk + d] = qv;
-    k_s[t * ldk + d] = kv;
+    q_t[d * LCP + t] = qv;
+    k_t[d * LCP + t] = kv;
   }
-  for (int i = tid; i < LC * cols; i += 256) {
-    const int t = i / cols, c = i - t * cols;
+  for (int i = tid; i < LC * 64; i += 256) {
+    const int t = i >> 6, c = i & 63;
     v_s[i] = (t < len && col0 + c < vdim)
                  ? silu(to_float(proj[(row0 + t) * row_stride + v_off + (long long)head * vdim + col0 + c])) : 0.f;
   }
   __syncthreads();
-  // a[t][s] = decay^(t-s) (q_t . k_s) for s <= t
-  for (int i = tid; i < LC * LC; i += 256) {
-    const int t = i / LC, s = i - t * LC;
-    float dot = 0.f;
-    if (s <= t && t < len) {
-      const float* qt = q_s + t * ldk;
-      const float* kr = k_s + s * ldk;
-      for (int d = 0; d < dim; ++d) dot = fmaf(qt[d], kr[d], dot);
-      dot *= pw[t - s];
+  // scores of the chunk: tokens t = 4 ty .. and s = 4 tx ..
+  {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    if (tx <= ty) {                      // (patches above the diagonal are zeros)
+      for (int d = 0; d < dim; ++d) {
+        const float4 qv = *reinterpret_cast<const float4*>(q_t + d * LCP + ty * 4);
+        const float4 kv = *reinterpret_cast<const float4*>(k_t + d * LCP + tx * 4);
+        const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qa[i], ka[j], acc[i][j]);
+      }
     }
-    a_s[t * (LC + 1) + s] = dot;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int sx = tx * 4 + j;
+      float4 o;
+      float* oa = reinterpret_cast<float*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = ty * 4 + i;
+        oa[i] = (sx <= t && t < len) ? acc[i][j] * pw[t - sx] : 0.f;
+      }
+      *reinterpret_cast<float4*>(a_t + sx * LCP + ty * 4) = o;
+    }
   }
   __syncthreads();
-  // thread = (row group, column): 256 / cols row groups, each with LC / groups tokens
-  const int groups = 256 / cols, gr = tid / cols, c = tid - gr * cols;
-  if (gr < groups && col0 + c < vdim) {
-    // the part of o_t that needs no earlier chunk
-    for (int t = gr; t < len; t += groups) {
-      float o = 0.f;
-      const float* at = a_s + t * (LC + 1);
-      for (int s = 0; s <= t; ++s) o = fmaf(at[s], v_s[s * cols + c], o);
-      out[(row0 + t) * out_row_stride + (long long)head * vdim + col0 + c] = o;
+  // the part of o_t that needs no earlier chunk: tokens 4 ty .., channels 4 tx ..
+  {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    const int s_end = min(len, ty * 4 + 4);
+    for (int sx = 0; sx < s_end; ++sx) {
+      const float4 av = *reinterpret_cast<const float4*>(a_t + sx * LCP + ty * 4);
+      const float4 vv = *reinterpret_cast<const float4*>(v_s + sx * 64 + tx * 4);
+      const float aa[4] = {av.x, av.y, av.z, av.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], va[j], acc[i][j]);
     }
-    // the chunk's contribution to the state: sum_s decay^(len-1-s) k_s[i] v_s[c]
-    float* dst = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim + col0 + c;
-    for (int i0 = gr; i0 < dim; i0 += groups) {
-      float kv = 0.f;
-      for (int s = 0; s < len; ++s) kv = fmaf(pw[len - 1 - s] * k_s[s * ldk + i0], v_s[s * cols + c], kv);
-      dst[(long long)i0 * vdim] = kv;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = ty * 4 + i;
+      if (t >= len) break;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = col0 + tx * 4 + j;
+        if (c < vdim) out[(row0 + t) * out_row_stride + (long long)head * vdim + c] = acc[i][j];
+      }
     }
+  }
+  // the chunk's contribution to the state: sum_s decay^(len-1-s) k_s[i] v_s[c], key channels 4 ty .. (+ 64, ...)
+  float* dst = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim;
+  for (int i0 = ty * 4; i0 < dim; i0 += 64) {
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int sx = 0; sx < len; ++sx) {
+      const float w = pw[len - 1 - sx];
+      const float4 vv = *reinterpret_cast<const float4*>(v_s + sx * 64 + tx * 4);
+      const float va[4] = {vv.x * w, vv.y * w, vv.z * w, vv.w * w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float kv = i0 + i < dim ? k_t[(i0 + i) * LCP + sx] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(kv, va[j], acc[i][j]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = col0 + tx * 4 + j;
+        if (i0 + i < dim && c < vdim) dst[(long long)(i0 + i) * vdim + c] = acc[i][j];
+      }
   }
 }
 
 // One thread per (sequence, head, state element): walks the sequence's chunks in order; leaves in scratch[chunk] the
-// state that chunk STARTS from and in `state` the state after the last one.
+// state that chunk STARTS from and in `state` the state after the last one.  Four chunks' contributions are asked for
+// at a time, so that the loads do not wait for one another.
 __global__ void __launch_bounds__(256)
-lightning_prefix_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ slots,
+lightning_prefix_kernel(float* scratch, float* __restrict__ state, const int* __restrict__ slots,
                         const int* __restrict__ seq_start, const float* __restrict__ decay, int max_chunks, int n_heads,
                         int dim, int vdim) {
   pdl_trigger();
@@ -229,14 +290,22 @@ lightning_prefix_kernel(float* __restrict__ scratch, float* __restrict__ state, 
   const int n_chunks = (n_new + LC - 1) / LC;
   const float lam = decay[head];
   const float full = powf(lam, (float)LC);
+  const float tail = powf(lam, (float)(n_new - (n_chunks - 1) * LC));
   float* st = state + (((long long)slots[seq] * n_heads + head) * dim) * vdim + e;
+  const long long stride = (long long)n_heads * dim * vdim;
+  float* cell = scratch + (((long long)seq * max_chunks) * n_heads + head) * (long long)dim * vdim + e;
   float s = *st;
-  for (int c = 0; c < n_chunks; ++c) {
-    float* cell = scratch + ((((long long)seq * max_chunks + c) * n_heads + head) * dim) * vdim + e;
-    const float kv = *cell;
-    *cell = s;
-    const int len = min(LC, n_new - c * LC);
-    s = fmaf(len == LC ? full : powf(lam, (float)len), s, kv);
+  for (int c = 0; c < n_chunks; c += 4) {
+    float kv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) kv[u] = c + u < n_chunks ? __ldcg(cell + (c + u) * stride) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (c + u < n_chunks) {
+        cell[(c + u) * stride] = s;
+        s = fmaf(c + u == n_chunks - 1 ? tail : full, s, kv[u]);
+      }
+    }
   }
   *st = s;
 }
@@ -248,38 +317,53 @@ lightning_carry_kernel(const T* __restrict__ proj, long long row_stride, int q_o
                        const float* __restrict__ decay, float* __restrict__ out, long long out_row_stride,
                        const float* __restrict__ scratch, int max_chunks, int n_heads, int dim, int vdim, int cols,
                        int col_blocks) {
-  extern __shared__ float sm[];
-  const int ldk = dim + 1;
-  float* q_s = sm;                 // [LC][ldk], already scaled by decay^(t+1)
-  float* s_s = q_s + LC * ldk;     // [dim][cols]
+  extern __shared__ __align__(16) float sm[];
+  float* q_t = sm;                 // [dim][LCP], q_t[d][t] already scaled by decay^(t+1)
+  float* s_s = q_t + dim * LCP;    // [dim][64]
   pdl_trigger();
   pdl_wait();
   const int chunk = blockIdx.x, seq = blockIdx.z;
-  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * cols;
+  const int head = blockIdx.y / col_blocks, col0 = (blockIdx.y - head * col_blocks) * 64;
   const int first = seq_start[seq], n_new = seq_start[seq + 1] - first;
   if (chunk * LC >= n_new) return;
   const int len = min(LC, n_new - chunk * LC);
   const long long row0 = first + (long long)chunk * LC;
   const float lam = decay[head];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   for (int i = tid; i < LC * dim; i += 256) {
     const int t = i / dim, d = i - t * dim;
-    q_s[t * ldk + d] = t < len ? silu(to_float(proj[(row0 + t) * row_stride + q_off + (long long)head * dim + d])) *
+    q_t[d * LCP + t] = t < len ? silu(to_float(proj[(row0 + t) * row_stride + q_off + (long long)head * dim + d])) *
                                      powf(lam, (float)(t + 1)) : 0.f;
   }
   const float* src = scratch + ((((long long)seq * max_chunks + chunk) * n_heads + head) * dim) * vdim + col0;
-  for (int i = tid; i < dim * cols; i += 256) {
-    const int d = i / cols, c = i - d * cols;
+  for (int i = tid; i < dim * 64; i += 256) {
+    const int d = i >> 6, c = i & 63;
     s_s[i] = col0 + c < vdim ? src[(long long)d * vdim + c] : 0.f;
   }
   __syncthreads();
-  const int groups = 256 / cols, gr = tid / cols, c = tid - gr * cols;
-  if (gr >= groups || col0 + c >= vdim) return;
-  for (int t = gr; t < len; t += groups) {
-    float o = 0.f;
-    const float* qt = q_s + t * ldk;
-    for (int d = 0; d < dim; ++d) o = fmaf(qt[d], s_s[d * cols + c], o);
-    out[(row0 + t) * out_row_stride + (long long)head * vdim + col0 + c] += o;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int d = 0; d < dim; ++d) {
+    const float4 qv = *reinterpret_cast<const float4*>(q_t + d * LCP + ty * 4);
+    const float4 sv = *reinterpret_cast<const float4*>(s_s + d * 64 + tx * 4);
+    const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, sa[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qa[i], sa[j], acc[i][j]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = ty * 4 + i;
+    if (t >= len) break;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx * 4 + j;
+      if (c < vdim) out[(row0 + t) * out_row_stride + (long long)head * vdim + c] += acc[i][j];
+    }
   }
 }
 
@@ -288,13 +372,13 @@ static int launch_lightning_chunked(const T* proj, long long row_stride, int q_o
                                     const int* slots, const int* seq_start, const float* decay, float* out,
                                     long long out_row_stride, float* scratch, int max_new, int n_seqs, int n_heads, int dim,
                                     int vdim, cudaStream_t stream) {
-  const int cols = vdim < 64 ? (vdim <= 32 ? 32 : 64) : 64;
+  const int cols = 64;
   const int col_blocks = (vdim + cols - 1) / cols;
   const int max_chunks = (max_new + LC - 1) / LC;
   BT_CHECK((long long)n_heads * col_blocks <= 65535, "lightning_scan: %d heads x %d column blocks are too many", n_heads, col_blocks);
   const dim3 grid(max_chunks, n_heads * col_blocks, n_seqs), block(256);
-  const size_t smem_a = ((size_t)2 * LC * (dim + 1) + (size_t)LC * cols + (size_t)LC * (LC + 1) + LC + 1) * sizeof(float);
-  const size_t smem_c = ((size_t)LC * (dim + 1) + (size_t)dim * cols) * sizeof(float);
+  const size_t smem_a = ((size_t)2 * dim * LCP + (size_t)LC * 64 + (size_t)LC * LCP + LC + 4) * sizeof(float);
+  const size_t smem_c = ((size_t)dim * LCP + (size_t)dim * 64) * sizeof(float);
   auto chunk_kernel = lightning_chunk_kernel<T>;
   auto carry_kernel = lightning_carry_kernel<T>;
   if (smem_a > 48 * 1024)

@@ -28,10 +28,23 @@ class Workspace:
         self.offset = 0
         self.frozen = False       # set while a CUDA graph is captured or replayed: addresses must not move
         self._retired: list[torch.Tensor] = []
+        self._moves = 0           # how often the buffer has been replaced by a larger one
 
     def reset(self) -> None:
         self.offset = 0
         self._retired.clear()
+
+    def mark(self):
+        """A point to come back to with `release`: what is taken after it can be handed out again."""
+        return (self._moves, self.offset)
+
+    def release(self, mark) -> None:
+        """Gives back everything taken since `mark`.  Only for pieces whose last use is a kernel already launched on the
+        step's own stream (later launches on that stream come after it); a part that hands work to a second stream
+        must not release what that work reads.  If the buffer was replaced meanwhile, nothing is given back."""
+        moves, offset = mark
+        if moves == self._moves and offset <= self.offset:
+            self.offset = offset
 
     _SIZES = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.float16: 2, torch.int64: 8, torch.uint8: 1}
 
@@ -50,6 +63,7 @@ class Workspace:
             self.buffer = torch.empty(max(2 * self.buffer.numel(), start + nbytes + (1 << 20)), dtype=torch.uint8,
                                       device=self.device)
             self._typed.clear()
+            self._moves += 1
             start = 0
         self.offset = start + nbytes
         flat = self._typed.get(dtype)

@@ -66,8 +66,10 @@ class GatedFeedForward(FeedForward):
             from ..engine.program import ProgramUnsupported
             raise ProgramUnsupported("a gated feed-forward has no phase in the fused step")
         n = ctx.n_tokens
+        mark = ctx.ws.mark()
         both = ctx.ws.take((n, 2 * self.inner), ctx.dtype)
         linear(ctx, x, self.t_gate_up_weight, None, both, m=n, w_is_nk=True)
         hidden = ctx.ws.take((n, self.inner), ctx.dtype)
         kernels.gated_activation(both, hidden, n_rows=n, activation=self.activation)
         linear(ctx, hidden, self.t_down_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+        ctx.ws.release(mark)

@@ -98,6 +98,7 @@ class LatentAttention(Mixer):
         if owns_cache != self.owns_latent:
             raise ShapeError("latent attention: a layer with its own latent projection owns its cache entry, and a "
                              "layer without one reads another layer's")
+        mark = ctx.ws.mark()      # (this layer's scratch is handed out again to the next one)
         n, dtype, heads = ctx.n_tokens, ctx.dtype, self.n_heads
         rank, rot, dk = self.kv_rank, self.rot_dim, self.latent_width
         proj = ctx.ws.take((n, self.in_width), dtype)
@@ -135,3 +136,4 @@ class LatentAttention(Mixer):
         kernels.head_linear(mixed_latent.view(n, heads, rank), self.uv_heads, mixed.view(n, heads, self.vdim), n_tokens=n,
                             gate=gate)
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+        ctx.ws.release(mark)

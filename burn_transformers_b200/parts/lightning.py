@@ -59,6 +59,7 @@ class LightningAttention(Mixer):
             raise ProgramUnsupported("lightning attention has no phase in the fused step")
         if not owns_cache:
             raise ShapeError("lightning attention: a recurrent state cannot be another layer's")
+        mark = ctx.ws.mark()      # (this layer's scratch is handed out again to the next one)
         n = ctx.n_tokens
         proj = ctx.ws.take((n, self.in_width), ctx.dtype)
         linear(ctx, x, self.t_in_weight, None, proj, m=n, w_is_nk=True)
@@ -74,3 +75,4 @@ class LightningAttention(Mixer):
         mixed = ctx.ws.take((n, self.v_width), ctx.dtype)
         kernels.rmsnorm(read, self.t_norm_weight, mixed, self.eps, n_rows=n, gate=proj[:, 2 * self.qk_width + self.v_width:])
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+        ctx.ws.release(mark)
