@@ -29,21 +29,30 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_row_stri
   const unsigned a_addr = ds_smem(a_s + (warp * 16 + (lane & 15)) * HL_LD + (lane >> 4) * 8);
   const int blk = lane >> 3;
   const unsigned w_addr = ds_smem(w_s + ((blk & 1) * 8 + (lane & 7)) * HL_LD + (blk >> 1) * 8);
+  // a piece of K travels global memory -> registers -> shared memory; the next piece is asked for before this one's
+  // products, so its flight is hidden behind them
+  uint4 a_reg[4], w_reg[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + u * 128, r = i >> 3, c = (i & 7) * 8;
+      a_reg[u] = (t0 + r < n_tokens && k0 + c < K)
+                     ? *reinterpret_cast<const uint4*>(ah + (long long)(t0 + r) * a_row_stride + k0 + c) : make_uint4(0u, 0u, 0u, 0u);
+      w_reg[u] = (k0 + r < K && n0 + c < N) ? *reinterpret_cast<const uint4*>(wh + (long long)(k0 + r) * N + n0 + c)
+                                            : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch(0);
   for (int k0 = 0; k0 < K; k0 += HL_BK) {
     __syncthreads();
-    for (int i = tid; i < HL_BM * (HL_BK / 8); i += 128) {
-      const int r = i >> 3, c = (i & 7) * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (t0 + r < n_tokens && k0 + c < K) v = *reinterpret_cast<const uint4*>(ah + (long long)(t0 + r) * a_row_stride + k0 + c);
-      *reinterpret_cast<uint4*>(a_s + r * HL_LD + c) = v;
-    }
-    for (int i = tid; i < HL_BK * (HL_BN / 8); i += 128) {
-      const int r = i >> 3, c = (i & 7) * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + r < K && n0 + c < N) v = *reinterpret_cast<const uint4*>(wh + (long long)(k0 + r) * N + n0 + c);
-      *reinterpret_cast<uint4*>(w_s + r * HL_LD + c) = v;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = tid + u * 128, r = i >> 3, c = (i & 7) * 8;
+      *reinterpret_cast<uint4*>(a_s + r * HL_LD + c) = a_reg[u];
+      *reinterpret_cast<uint4*>(w_s + r * HL_LD + c) = w_reg[u];
     }
     __syncthreads();
+    if (k0 + HL_BK < K) fetch(k0 + HL_BK);
 #pragma unroll
     for (int ks = 0; ks < HL_BK / 16; ++ks) {
       unsigned af[4];

@@ -50,7 +50,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_row
   pdl_trigger();
   pdl_wait();
   const int seq = blockIdx.z, split = blockIdx.y;
-  const int token_tile = blockIdx.x / head_tiles, head_tile = blockIdx.x - token_tile * head_tiles;
+  // (the last tokens of a prompt see the most keys: their tiles come first, so that the longest blocks start first)
+  const int token_tiles = gridDim.x / head_tiles;
+  const int token_tile = token_tiles - 1 - blockIdx.x / head_tiles, head_tile = blockIdx.x % head_tiles;
   const int first = seq_start[seq], n_new = seq_start[seq + 1] - first, past = past_len[seq];
   const int t0 = token_tile * tq;
   if (t0 >= n_new) return;
@@ -134,6 +136,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_row
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
       const unsigned k_addr = ds_smem(kt + (key_base + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+#pragma unroll 2
       for (int ks = 0; ks < dkp / 16; ++ks) {
         unsigned a[4];
         ds_ldmatrix_x4(a, q_addr + ks * 32);
