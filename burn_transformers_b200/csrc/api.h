@@ -88,6 +88,15 @@ int bt_latent_append(const void* src, long long row_stride, const float* norm_we
                      const int* token_seq, const float* inv_freq, int rot_dims, const int* table, int table_stride,
                      int table_len, int page_size, void* pool, int n_tokens, int rank, int rot, int dtype,
                      cudaStream_t stream);
+int bt_latent_gather(const void* pool, const int* positions, const int* token_seq, const int* table, int table_stride,
+                     int table_len, int page_size, void* rows, int n_tokens, int dk, int dtype, cudaStream_t stream);
+// Causal multi-head attention of fresh prompts on tensor cores with a sink and a gate (csrc/sink_attention_mma.cu).
+int bt_sink_attention_supports(int dq, int dv, long long q_row, int q_head, long long k_row, int k_head, long long v_row,
+                               int v_head, long long gate_row, int gate_head, long long out_row, int out_head);
+int bt_sink_attention(const void* q, long long q_row, int q_head, const void* k, long long k_row, int k_head,
+                      const void* v, long long v_row, int v_head, const void* gate, long long gate_row, int gate_head,
+                      void* out, long long out_row, int out_head, const int* seq_start, const float* sink, int n_seqs,
+                      int max_new, int n_heads, int dq, int dv, float scale, cudaStream_t stream);
 int bt_head_linear(const void* a, long long a_row_stride, int a_head_stride, const void* w, void* out,
                    long long out_row_stride, int out_head_stride, const void* gate, long long gate_row_stride,
                    int gate_head_stride, int n_tokens, int n_heads, int K, int N, int tensor_cores, int dtype,

@@ -78,6 +78,22 @@ latent_append_kernel(const T* __restrict__ src, long long row_stride, const floa
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = row[rank + c];
 }
 
+// rows[t] = the cached row of token t's own position (for steps that want the latents of their tokens side by side)
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_gather_kernel(const T* __restrict__ pool, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                     const int* __restrict__ table, int table_stride, int table_len, int page_size, T* __restrict__ rows,
+                     int dk) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = token_seq[t], pos = positions[t];
+  const int lp = pos / page_size;
+  const int page = table[(long long)seq * table_stride + (lp % table_len)];
+  const T* src = pool + ((long long)page * page_size + (pos - lp * page_size)) * dk;
+  for (int c = threadIdx.x; c < dk; c += blockDim.x) rows[(long long)t * dk + c] = src[c];
+}
+
 // ---- per-head products ------------------------------------------------------------------------------------------
 
 // out[t, h, j] = sum_k a[t, h, k] * W[h][k][j]   (* sigmoid(gate[t, h, j]) if gate)
@@ -402,6 +418,25 @@ extern "C" int bt_latent_append(const void* src, long long row_stride, const flo
                                           (__nv_bfloat16*)pool, rank, rot));
   else
     return fail("latent_append: unknown dtype %d", dtype);
+  return 0;
+}
+
+extern "C" int bt_latent_gather(const void* pool, const int* positions, const int* token_seq, const int* table,
+                                int table_stride, int table_len, int page_size, void* rows, int n_tokens, int dk, int dtype,
+                                cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(dk > 0 && table_len > 0 && page_size > 0, "latent_gather: bad sizes dk=%d table_len=%d", dk, table_len);
+  if (n_tokens == 0) return 0;
+  if (dtype == kF32)
+    BT_PDL_OK("latent_gather", launch_pdl(latent_gather_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                                          (const float*)pool, positions, token_seq, table, table_stride, table_len,
+                                          page_size, (float*)rows, dk));
+  else if (dtype == kBF16)
+    BT_PDL_OK("latent_gather", launch_pdl(latent_gather_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, 1,
+                                          (const __nv_bfloat16*)pool, positions, token_seq, table, table_stride, table_len,
+                                          page_size, (__nv_bfloat16*)rows, dk));
+  else
+    return fail("latent_gather: unknown dtype %d", dtype);
   return 0;
 }
 

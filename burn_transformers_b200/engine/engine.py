@@ -5,7 +5,7 @@ next tokens (a whole prompt, or one token) and runs exactly those tokens against
 earlier steps left; it returns the 32-bit logits at the wanted places.  Sequences of different
 lengths are packed one after another, so there is no padding and nothing to mask out.
 
-The contract follows the reference's prefill/decode pair (src/architecture/traits.rs:110-153,
+The semantics of a step follow the reference's prefill/decode pair (src/architecture/traits.rs:110-153,
 src/models/shared/rows.rs:1-45 of NoahIsCool/burn-transformers): positions of new tokens continue
 the sequence's length, requests are validated before the cache changes, and lengths advance only
 when the step has been issued.

@@ -50,7 +50,7 @@ class KernelProfile:
 
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
             "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats",
-            "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats")
+            "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats", "bt_sink_attention_supports")
 
     def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
@@ -837,3 +837,59 @@ def scale_(x, factor: float):
     """x *= factor for a contiguous 32-bit tensor."""
     _need(x, "x", torch.float32)
     _check(library().bt_scale(_ptr(x), c_longlong(x.numel()), c_float(factor), _stream()))
+
+
+def latent_gather(pool, positions, token_seq, table, table_len, rows, *, n_tokens):
+    """rows[t] = the cached row at token t's own position: the step's latent rows side by side."""
+    dk = pool.shape[2]
+    _need(pool, "pool", (torch.float32, torch.bfloat16), (None, PAGE_SIZE, dk))
+    _need(rows, "rows", pool.dtype, (None, dk))
+    _need(table, "table", torch.int32)
+    if rows.shape[0] < n_tokens:
+        raise ShapeError(f"latent_gather: {n_tokens} tokens asked of rows[{rows.shape[0]}]")
+    _work(0.0, 2.0 * n_tokens * dk * pool.element_size())
+    _check(library().bt_latent_gather(_ptr(pool), _ptr(positions), _ptr(token_seq), _ptr(table), c_int(table.shape[1]),
+                                      c_int(table_len), c_int(PAGE_SIZE), _ptr(rows), c_int(n_tokens), c_int(dk),
+                                      c_int(_code(pool.dtype)), _stream()))
+
+
+def _sink_attention_strides(q, k, v, gate, out):
+    heads = q.shape[1]
+    strides = []
+    for name, t, width in (("q", q, q.shape[2]), ("k", k, q.shape[2]), ("v", v, v.shape[2]),
+                           ("gate", gate, v.shape[2]), ("out", out, v.shape[2])):
+        strides.append((0, 0) if t is None else _head_view(t, name, heads, width))
+    return strides
+
+
+def sink_attention_supports(q, k, v, gate, out) -> bool:
+    """Whether sink_attention takes these views: bfloat16, whole 16-byte pieces per head and token, at most 128 value
+    channels, operands on 16-byte boundaries."""
+    if any(t is not None and t.dtype is not torch.bfloat16 for t in (q, k, v, gate, out)):
+        return False
+    (qr, qh), (kr, kh), (vr, vh), (gr, gh), (orow, oh) = _sink_attention_strides(q, k, v, gate, out)
+    if any(t.data_ptr() % 16 for t in (q, k, v)) or out.data_ptr() % 4 or (gate is not None and gate.data_ptr() % 4):
+        return False
+    return bool(library().bt_sink_attention_supports(c_int(q.shape[2]), c_int(v.shape[2]), c_longlong(qr), c_int(qh),
+                                                     c_longlong(kr), c_int(kh), c_longlong(vr), c_int(vh), c_longlong(gr),
+                                                     c_int(gh), c_longlong(orow), c_int(oh)))
+
+
+def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None, gate=None):
+    """Causal multi-head attention of sequences that start at position 0, on tensor cores (bfloat16): token t of a
+    sequence sees the sequence's tokens up to itself.  q, k: views [tokens, heads, dq]; v, out, gate: views
+    [tokens, heads, dv].  `sink` [heads] adds exp(sink_h) to head h's softmax denominator; `gate` multiplies the result by
+    sigmoid(gate).  Scores, softmax and sums are 32-bit."""
+    heads, dq, dv = q.shape[1], q.shape[2], v.shape[2]
+    if not sink_attention_supports(q, k, v, gate, out):
+        raise ShapeError("sink_attention: the kernel does not take these views (see sink_attention_supports)")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (heads,))
+    (qr, qh), (kr, kh), (vr, vh), (gr, gh), (orow, oh) = _sink_attention_strides(q, k, v, gate, out)
+    if _PROFILE is not None:
+        ctx = float(_PROFILE.context_hint or 0)
+        _work(2.0 * q.shape[0] * heads * (ctx / 2) * (dq + dv), 2.0 * q.shape[0] * heads * (2 * dq + 2 * dv))
+    _check(library().bt_sink_attention(_ptr(q), c_longlong(qr), c_int(qh), _ptr(k), c_longlong(kr), c_int(kh), _ptr(v),
+                                       c_longlong(vr), c_int(vh), _ptr(gate), c_longlong(gr), c_int(gh), _ptr(out),
+                                       c_longlong(orow), c_int(oh), _ptr(seq_start), _ptr(sink), c_int(n_seqs),
+                                       c_int(max_new), c_int(heads), c_int(dq), c_int(dv), c_float(scale), _stream()))

@@ -38,6 +38,11 @@ class LatentAttention(Mixer):
     """
 
     accepts_lazy_norm = True
+    # Prompts of sequences that start at position 0 and bring at least this many tokens take the plain form in bfloat16:
+    # keys and values up-projected per head for the step's tokens, then multi-head attention (dim + rot_dim + vdim
+    # multiply-adds a key and head instead of 2 kv_rank + rot_dim).  Everything else (decode steps, portions that continue a
+    # sequence, 32-bit) reads the latent rows directly.
+    plain_from = 48
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
                  positions, *, owns_latent: bool = True, sink: bool = True, init_std: float = 0.02,
@@ -76,6 +81,7 @@ class LatentAttention(Mixer):
         # ([kv_rank, vdim])
         self.uk_heads = self.t_uk_weight.view(self.n_heads, self.dim, self.kv_rank)
         self.uv_heads = self.t_uv_weight.view(self.n_heads, self.vdim, self.kv_rank).transpose(1, 2).contiguous()
+        self.uk_heads_t = self.uk_heads.transpose(1, 2).contiguous()       # [heads, kv_rank, dim]: latent -> plain key
         self.positions.inv_freq(self.t_uk_weight.device)
 
     def cache_need(self):
@@ -114,8 +120,31 @@ class LatentAttention(Mixer):
             kernels.latent_append(proj[:, self.q_width + self.gate_width:], self.t_latent_norm_weight, self.eps,
                                   ctx.positions, ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool,
                                   n, rank, rot)
-        # the queries as the latent rows meet them: per head [W_uk^T q_plain | q_rot turned]
         q_heads = proj[:, :self.q_width].view(n, heads, self.dim + rot)
+        gate = proj[:, self.q_width:self.q_width + self.gate_width].view(n, heads, self.vdim)
+        if dtype == torch.bfloat16 and ctx.fresh and not ctx.is_decode and ctx.max_new >= self.plain_from:
+            # fresh prompts: the step's own latent rows, keys and values per head, ordinary attention
+            rows = ctx.ws.take((n, dk), dtype)
+            keys = ctx.ws.take((n, heads, self.dim + rot), dtype)
+            values = ctx.ws.take((n, heads, self.vdim), dtype)
+            mixed = ctx.ws.take((n, self.gate_width), dtype)
+            mixed_heads = mixed.view(n, heads, self.vdim)
+            if kernels.sink_attention_supports(q_heads, keys, values, gate, mixed_heads):
+                kernels.latent_gather(pool, ctx.positions, ctx.token_seq, table, group.table_len, rows, n_tokens=n)
+                latent = rows[:, :rank].unsqueeze(1).expand(n, heads, rank)
+                kernels.head_linear(latent, self.uk_heads_t, keys[:, :, :self.dim], n_tokens=n)
+                kernels.head_linear(latent, self.uv_heads, values, n_tokens=n)
+                if rot:
+                    shared = rows[:, rank:].unsqueeze(1).expand(n, heads, rot)
+                    kernels.rotary_interleaved(shared, keys[:, :, self.dim:], ctx.positions, freq, n_tokens=n, dims=0)
+                    self.positions.rotate_vectors(ctx, q_heads[:, :, self.dim:], q_heads[:, :, self.dim:])
+                kernels.sink_attention(q_heads, keys, values, mixed_heads, ctx.seq_start, n_seqs=ctx.n_seqs,
+                                       max_new=ctx.max_new, scale=self.scale,
+                                       sink=self.t_sink if self.has_sink else None, gate=gate)
+                linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+                ctx.ws.release(mark)
+                return
+        # the queries as the latent rows meet them: per head [W_uk^T q_plain | q_rot turned]
         q_latent = ctx.ws.take((n, heads * dk), dtype)
         q_latent_heads = q_latent.view(n, heads, dk)
         kernels.head_linear(q_heads[:, :, :self.dim], self.uk_heads, q_latent_heads[:, :, :rank], n_tokens=n)
@@ -132,7 +161,6 @@ class LatentAttention(Mixer):
                                  scratch=scratch)
         # values: W_uv on the weighted latents, times the output gate
         mixed = ctx.ws.take((n, self.gate_width), dtype)
-        gate = proj[:, self.q_width:self.q_width + self.gate_width].view(n, heads, self.vdim)
         kernels.head_linear(mixed_latent.view(n, heads, rank), self.uv_heads, mixed.view(n, heads, self.vdim), n_tokens=n,
                             gate=gate)
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)

@@ -106,6 +106,20 @@ def test_long_decoding_from_the_first_token(case, dtype):
     assert len(got) == len(seqs[long]) and err < TOL[dtype], f"{err:.3e} at {where}"
 
 
+@pytest.mark.parametrize("plain_from", [1, 10 ** 9])
+def test_both_forms_of_prompt_attention(case, plain_from, monkeypatch):
+    """bfloat16 prompts of fresh sequences take the plain form (keys and values per head) from a length on and read the
+    latent rows directly below it: each form alone, over all lengths, against the plain implementation; then decoding on
+    top of a prompt that went through the plain form."""
+    from burn_transformers_b200.parts import LatentAttention
+    monkeypatch.setattr(LatentAttention, "plain_from", plain_from)
+    _, folder, seqs, ref = case
+    engine = engine_for(folder, "bfloat16")
+    for got in (replay.whole(engine, seqs), replay.tail_one_by_one(engine, seqs, tail=5)):
+        err, where = replay.worst_error(got, ref)
+        assert err < TOL["bfloat16"], f"{err:.3e} at {where}"
+
+
 def test_a_released_slot_starts_from_an_empty_state(case):
     """A sequence that takes over a slot finds neither the old recurrent state nor the old latent rows."""
     _, folder, seqs, ref = case

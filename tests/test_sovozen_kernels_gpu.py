@@ -265,3 +265,48 @@ def test_recurrence_carries_its_state_from_step_to_step(dtype, tol, heads, dim, 
         assert rel(host(out[:n]), expect) < tol and bool((out[n:] == 0).all())
         fed = [f + m for f, m in zip(fed, step)]
     assert bool((state[1] == 4.0).all()) and bool((state[[2, 4, 6]] == 0).all())
+
+
+@pytest.mark.parametrize("heads, dq, dv", [(3, 48, 40), (2, 96, 64), (1, 136, 128), (5, 16, 8)])
+@pytest.mark.parametrize("with_sink, with_gate", [(True, True), (False, False)])
+def test_attention_of_fresh_prompts_with_a_sink_and_a_gate(heads, dq, dv, with_sink, with_gate):
+    """Sequences of 1, 33, 64, 65 and 200 tokens in one call, heads as strided views of wider rows: every row against the
+    plain softmax over the keys up to its own position."""
+    rng = np.random.default_rng(dq)
+    lengths = [65, 1, 200, 33, 64]
+    n = sum(lengths)
+    wide = dev(rng.standard_normal((n, heads * (dq + 8) + 16)) * 0.6, torch.bfloat16)
+    q = wide[:, 16:].view(n, heads, dq + 8)[:, :, 8:]
+    k = dev(rng.standard_normal((n, heads, dq)) * 0.6, torch.bfloat16)
+    v = dev(rng.standard_normal((n, heads, dv)), torch.bfloat16)
+    gate = dev(rng.standard_normal((n, heads, dv)), torch.bfloat16) if with_gate else None
+    sink = rng.standard_normal(heads) * 2.0
+    out = torch.zeros((n + 1, heads, dv), dtype=torch.bfloat16, device=DEV)
+    seq_start = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    assert kernels.sink_attention_supports(q, k, v, gate, out[:n])
+    kernels.sink_attention(q, k, v, out[:n], torch.tensor(seq_start, device=DEV), n_seqs=len(lengths),
+                           max_new=max(lengths), scale=0.17, sink=dev(sink) if with_sink else None, gate=gate)
+    qh, kh, vh = host(q), host(k), host(v)
+    want = np.zeros((n, heads, dv))
+    for s, length in enumerate(lengths):
+        lo = seq_start[s]
+        for h in range(heads):
+            scores = (qh[lo:lo + length, h] @ kh[lo:lo + length, h].T) * 0.17
+            scores = np.where(np.tril(np.ones((length, length), dtype=bool)), scores, -np.inf)
+            want[lo:lo + length, h] = plain.sink_softmax_mix(scores, sink[h] if with_sink else -np.inf, vh[lo:lo + length, h])
+    if with_gate:
+        want = want * plain.sigmoid(host(gate))
+    assert rel(host(out[:n]), want) < 2e-2 and bool((out[n:] == 0).all())
+
+
+def test_gather_of_the_steps_own_latent_rows():
+    rng = np.random.default_rng(4)
+    dk = 40
+    pool = dev(rng.standard_normal((9, 64, dk)), torch.bfloat16)
+    positions = torch.tensor([0, 63, 64, 130, 5], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 8, 0], [1, 4, 6]], dtype=torch.int32, device=DEV)
+    rows = torch.zeros((6, dk), dtype=torch.bfloat16, device=DEV)
+    kernels.latent_gather(pool, positions, token_seq, table, 3, rows, n_tokens=5)
+    want = torch.stack([pool[3, 0], pool[3, 63], pool[8, 0], pool[6, 2], pool[1, 5]])
+    assert torch.equal(rows[:5], want) and bool((rows[5] == 0).all())
