@@ -105,8 +105,17 @@ long long bt_latent_attention_scratch_floats(int n_tokens, int n_heads, int rank
 int bt_latent_attention(const void* q, long long q_row_stride, const void* pool, const int* table, int table_stride,
                         int table_len, int page_size, const int* seq_start, const int* past_len, const float* sink,
                         void* out, long long out_row_stride, float* part, int n_tokens, int n_seqs, int max_new,
-                        int n_heads, int rank, int rot, float scale, int n_splits, int tensor_cores, int dtype,
+                        int n_heads, int rank, int rot, float scale, int n_splits, int tensor_cores, int merge, int dtype,
                         cudaStream_t stream);
+// The steps around the latent attention fused for steps of few tokens (csrc/latent_decode.cu).
+int bt_latent_decode_prep(const void* proj, long long row_stride, int q_off, int latent_off, const void* uk,
+                          const float* norm_weight, float eps, const int* positions, const int* token_seq,
+                          const float* inv_freq, int rot_dims, const int* table, int table_stride, int table_len,
+                          int page_size, void* pool, void* q_latent, int n_tokens, int n_heads, int dim, int rank, int rot,
+                          int owns, int dtype, cudaStream_t stream);
+int bt_latent_decode_finish(const float* part, const void* mixed_latent, int n_splits, const void* uv, const void* gate,
+                            long long gate_row_stride, void* out, long long out_row_stride, int n_tokens, int n_heads,
+                            int rank, int vdim, int dtype, cudaStream_t stream);
 int bt_latent_attention_rows(int rank, int rot, int dtype, int tensor_cores);
 int bt_lightning_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, float* state,
                       const int* slots, const int* seq_start, const float* decay, float* out, long long out_row_stride,

@@ -480,7 +480,8 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
                                    int table_stride, int table_len, int page_size, const int* seq_start,
                                    const int* past_len, const float* sink, void* out, long long out_row_stride,
                                    float* part, int n_tokens, int n_seqs, int max_new, int n_heads, int rank, int rot,
-                                   float scale, int n_splits, int tensor_cores, int dtype, cudaStream_t stream) {
+                                   float scale, int n_splits, int tensor_cores, int merge, int dtype,
+                                   cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && rank > 0 && rot >= 0 && rank <= 512, "latent_attention: bad sizes heads=%d rank=%d rot=%d (rank "
            "at most 512)", n_heads, rank, rot);
@@ -495,6 +496,7 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
                                                out_row_stride, part, n_tokens, n_seqs, max_new, n_heads, rank, rot, scale,
                                                n_splits, stream))
       return e;
+    if (!merge) return 0;
     return launch_latent_merge<float>(part, (float*)out, out_row_stride, n_tokens, n_heads, rank, n_splits, stream);
   }
   if (dtype == kBF16) {
@@ -508,7 +510,7 @@ extern "C" int bt_latent_attention(const void* q, long long q_row_stride, const 
                                                  table_stride, table_len, page_size, seq_start, past_len, sink,
                                                  (__nv_bfloat16*)out, out_row_stride, part, n_tokens, n_seqs, max_new,
                                                  n_heads, rank, rot, scale, n_splits, stream);
-    if (e) return e;
+    if (e || !merge) return e;
     return launch_latent_merge<__nv_bfloat16>(part, (__nv_bfloat16*)out, out_row_stride, n_tokens, n_heads, rank,
                                               n_splits, stream);
   }

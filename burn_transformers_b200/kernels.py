@@ -709,7 +709,7 @@ def latent_attention_rows(rank, rot, dtype, tensor_cores=True) -> int:
 
 
 def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_tokens, n_seqs, max_new, n_heads, rank,
-                     rot, scale, sink=None, n_splits=1, scratch=None, tensor_cores=True):
+                     rot, scale, sink=None, n_splits=1, scratch=None, tensor_cores=True, merge=True):
     """Causal attention of the step's tokens over their sequences' latent pages.
 
     q: [tokens, heads * (rank + rot)] (per head: the query carried into the latent space, then its rotated part);
@@ -717,7 +717,8 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
     `sink` [heads] (32-bit) adds exp(sink_h) to head h's denominator.  With `n_splits` > 1 the keys of a row tile are
     cut into that many runs whose partial results meet in `scratch` (32-bit, latent_attention_scratch_floats).
     bfloat16 runs on tensor cores where the shape allows it (rank + rot a multiple of 8, rank a multiple of 8, 16 or 32
-    up to 128, 256, 512); `tensor_cores=False` keeps it on the 32-bit multiply-add kernel that every other case takes."""
+    up to 128, 256, 512); `tensor_cores=False` keeps it on the 32-bit multiply-add kernel that every other case takes.
+    `merge=False` (with splits) leaves the partial results in `scratch` for latent_decode_finish to join."""
     dk = rank + rot
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * dk))
     _need(out, "out", q.dtype, (None, n_heads * rank))
@@ -742,8 +743,8 @@ def latent_attention(q, out, pool, table, table_len, seq_start, past_len, *, n_t
         _ptr(q), c_longlong(q.shape[1]), _ptr(pool), _ptr(table), c_int(table.shape[1]), c_int(table_len),
         c_int(PAGE_SIZE), _ptr(seq_start), _ptr(past_len), _ptr(sink), _ptr(out), c_longlong(out.shape[1]),
         _ptr(scratch if n_splits > 1 else None), c_int(n_tokens), c_int(n_seqs), c_int(max_new), c_int(n_heads),
-        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(1 if tensor_cores else 0), c_int(_code(q.dtype)),
-        _stream()))
+        c_int(rank), c_int(rot), c_float(scale), c_int(n_splits), c_int(1 if tensor_cores else 0),
+        c_int(1 if merge else 0), c_int(_code(q.dtype)), _stream()))
 
 
 LIGHTNING_CHUNK = 64      # runs of more new tokens than this take the chunked form of the recurrence
@@ -893,3 +894,53 @@ def sink_attention(q, k, v, out, seq_start, *, n_seqs, max_new, scale, sink=None
                                        c_longlong(vr), c_int(vh), _ptr(gate), c_longlong(gr), c_int(gh), _ptr(out),
                                        c_longlong(orow), c_int(oh), _ptr(seq_start), _ptr(sink), c_int(n_seqs),
                                        c_int(max_new), c_int(heads), c_int(dq), c_int(dv), c_float(scale), _stream()))
+
+
+def latent_decode_prep(proj, q_off, latent_off, uk_heads, norm_weight, eps, positions, token_seq, inv_freq, rot_dims, table,
+                       table_len, pool, q_latent, *, n_tokens, n_heads, dim, rank, rot, owns):
+    """For steps of few tokens, in one launch: q_latent[t, h] = [W_uk,h^T q_plain | q_rot turned by the position], and
+    (if `owns`) the token's own latent row normed, turned and filed in its page.  proj: [tokens, width] rows with the
+    queries at `q_off` (per head dim + rot channels) and the latent row at `latent_off`; uk_heads: [heads, dim, rank]."""
+    _need(proj, "proj", (torch.float32, torch.bfloat16))
+    _need(uk_heads, "uk_heads", proj.dtype, (n_heads, dim, rank))
+    _need(pool, "pool", proj.dtype, (None, PAGE_SIZE, rank + rot))
+    _need(q_latent, "q_latent", proj.dtype, (None, n_heads * (rank + rot)))
+    _need(inv_freq, "inv_freq", torch.float32)
+    if owns:
+        _need(norm_weight, "norm_weight", torch.float32, (rank,))
+    if q_off + n_heads * (dim + rot) > proj.shape[1] or (owns and latent_off + rank + rot > proj.shape[1]):
+        raise ShapeError("latent_decode_prep: the channel offsets leave the rows of proj")
+    if proj.shape[0] < n_tokens or q_latent.shape[0] < n_tokens or inv_freq.numel() < rot_dims // 2:
+        raise ShapeError("latent_decode_prep: too few rows or frequencies")
+    _check(library().bt_latent_decode_prep(_ptr(proj), c_longlong(proj.shape[1]), c_int(q_off), c_int(latent_off),
+                                           _ptr(uk_heads), _ptr(norm_weight if owns else None), c_float(eps),
+                                           _ptr(positions), _ptr(token_seq), _ptr(inv_freq), c_int(rot_dims), _ptr(table),
+                                           c_int(table.shape[1]), c_int(table_len), c_int(PAGE_SIZE), _ptr(pool),
+                                           _ptr(q_latent), c_int(n_tokens), c_int(n_heads), c_int(dim), c_int(rank),
+                                           c_int(rot), c_int(1 if owns else 0), c_int(_code(proj.dtype)), _stream()))
+
+
+def latent_decode_finish(uv_heads, out, *, n_tokens, n_splits, scratch=None, mixed_latent=None, gate=None):
+    """For steps of few tokens, in one launch: joins the `n_splits` partial results of latent_attention(merge=False) in
+    `scratch` (or reads `mixed_latent` [tokens, heads * rank] when there was one split), multiplies each head's weighted
+    latent by uv_heads[h] ([heads, rank, vdim]) and by sigmoid(gate).  out: [tokens, heads * vdim]; gate: a view
+    [tokens, heads * vdim] with contiguous channels."""
+    n_heads, rank, vdim = uv_heads.shape
+    _need(uv_heads, "uv_heads", (torch.float32, torch.bfloat16), (n_heads, rank, vdim))
+    _need(out, "out", uv_heads.dtype, (None, n_heads * vdim))
+    if n_splits > 1:
+        need = latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise ShapeError(f"latent_decode_finish: {n_splits} splits leave {need} floats of partial results")
+    else:
+        _need(mixed_latent, "mixed_latent", uv_heads.dtype, (None, n_heads * rank))
+    g_rs = 0
+    if gate is not None:
+        if gate.dim() != 2 or gate.shape[1] != n_heads * vdim or gate.stride(1) != 1 or gate.dtype is not uv_heads.dtype:
+            raise ShapeError("latent_decode_finish: gate must be a view [tokens, heads * vdim] of the weights' type")
+        g_rs = gate.stride(0)
+    _check(library().bt_latent_decode_finish(_ptr(scratch if n_splits > 1 else None),
+                                             _ptr(mixed_latent if n_splits == 1 else None), c_int(n_splits), _ptr(uv_heads),
+                                             _ptr(gate), c_longlong(g_rs), _ptr(out), c_longlong(out.shape[1]),
+                                             c_int(n_tokens), c_int(n_heads), c_int(rank), c_int(vdim),
+                                             c_int(_code(uv_heads.dtype)), _stream()))

@@ -43,6 +43,9 @@ class LatentAttention(Mixer):
     # multiply-adds a key and head instead of 2 kv_rank + rot_dim).  Everything else (decode steps, portions that continue a
     # sequence, 32-bit) reads the latent rows directly.
     plain_from = 48
+    # Steps of at most this many tokens (decode steps) run the steps around the attention as two fused kernels
+    # (csrc/latent_decode.cu) instead of five launches.
+    fused_up_to = 64
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float, eps: float,
                  positions, *, owns_latent: bool = True, sink: bool = True, init_std: float = 0.02,
@@ -116,6 +119,30 @@ class LatentAttention(Mixer):
         pool = k_pool.view(-1, PAGE_SIZE, dk)
         table = ctx.tables[g]
         freq = self.positions.inv_freq(proj.device)
+        if n <= self.fused_up_to:
+            # few tokens: query into the latent space + rotation + filing in one launch, the attention, then
+            # join of the splits + W_uv + gate in one launch
+            q_latent = ctx.ws.take((n, heads * dk), dtype)
+            kernels.latent_decode_prep(proj, 0, self.q_width + self.gate_width, self.uk_heads,
+                                       self.t_latent_norm_weight if self.owns_latent else None, self.eps, ctx.positions,
+                                       ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool, q_latent,
+                                       n_tokens=n, n_heads=heads, dim=self.dim, rank=rank, rot=rot, owns=self.owns_latent)
+            mixed_latent = ctx.ws.take((n, heads * rank), dtype)
+            splits = self._splits(ctx, kernels.latent_attention_rows(rank, rot, dtype))
+            scratch = None
+            if splits > 1:
+                scratch = ctx.ws.take((kernels.latent_attention_scratch_floats(n, heads, rank, splits),), torch.float32)
+            kernels.latent_attention(q_latent, mixed_latent, pool, table, group.table_len, ctx.seq_start, ctx.past_len,
+                                     n_tokens=n, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, rank=rank, rot=rot,
+                                     scale=self.scale, sink=self.t_sink if self.has_sink else None, n_splits=splits,
+                                     scratch=scratch, merge=False)
+            mixed = ctx.ws.take((n, self.gate_width), dtype)
+            kernels.latent_decode_finish(self.uv_heads, mixed, n_tokens=n, n_splits=splits, scratch=scratch,
+                                         mixed_latent=mixed_latent,
+                                         gate=proj[:, self.q_width:self.q_width + self.gate_width])
+            linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
+            ctx.ws.release(mark)
+            return
         if self.owns_latent:
             kernels.latent_append(proj[:, self.q_width + self.gate_width:], self.t_latent_norm_weight, self.eps,
                                   ctx.positions, ctx.token_seq, freq, self.positions.dims, table, group.table_len, pool,

@@ -310,3 +310,70 @@ def test_gather_of_the_steps_own_latent_rows():
     kernels.latent_gather(pool, positions, token_seq, table, 3, rows, n_tokens=5)
     want = torch.stack([pool[3, 0], pool[3, 63], pool[8, 0], pool[6, 2], pool[1, 5]])
     assert torch.equal(rows[:5], want) and bool((rows[5] == 0).all())
+
+
+@pytest.mark.parametrize("dtype, tol", DTYPES)
+@pytest.mark.parametrize("owns", [True, False])
+def test_fused_steps_before_the_attention_of_few_tokens(dtype, tol, owns):
+    """One launch: the query carried into the latent space, its rotated part turned, and (for a layer with a latent of its
+    own) the token's latent row normed, turned and filed."""
+    rng = np.random.default_rng(12)
+    n, heads, dim, rank, rot, dims = 5, 3, 20, 24, 10, 6
+    q_off, lat_off = 0, heads * (dim + rot) + 7
+    proj = dev(rng.standard_normal((n, lat_off + rank + rot + 3)), dtype)
+    uk = dev(rng.standard_normal((heads, dim, rank)) / np.sqrt(dim), dtype)
+    weight = dev(1.0 + 0.2 * rng.standard_normal(rank))
+    freq = torch.tensor([30.0 ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float32, device=DEV)
+    positions = np.asarray([63, 64, 200, 0, 7], dtype=np.int32)
+    token_seq = np.asarray([0, 1, 2, 3, 4], dtype=np.int32)
+    table = rng.permutation(20).reshape(5, 4).astype(np.int32)
+    pool = torch.full((20, 64, rank + rot), 5.0, dtype=dtype, device=DEV)
+    q_latent = torch.zeros((n + 1, heads * (rank + rot)), dtype=dtype, device=DEV)
+    kernels.latent_decode_prep(proj, q_off, lat_off, uk, weight if owns else None, 1e-4, torch.tensor(positions, device=DEV),
+                               torch.tensor(token_seq, device=DEV), freq, dims, torch.tensor(table, device=DEV), 4, pool,
+                               q_latent, n_tokens=n, n_heads=heads, dim=dim, rank=rank, rot=rot, owns=owns)
+    p = host(proj)
+    q = p[:, :heads * (dim + rot)].reshape(n, heads, dim + rot)
+    want = np.concatenate([np.einsum("thd,hdr->thr", q[:, :, :dim], host(uk)),
+                           plain.rotate_interleaved(q[:, :, dim:], positions, dims, 30.0)], axis=-1)
+    assert rel(host(q_latent[:n]).reshape(n, heads, rank + rot), want) < tol and bool((q_latent[n:] == 0).all())
+    written = torch.zeros_like(pool, dtype=torch.bool)
+    if owns:
+        lat = p[:, lat_off:lat_off + rank + rot]
+        want_c = plain.rms_norm(lat[:, :rank], host(weight), 1e-4)
+        want_r = plain.rotate_interleaved(lat[:, rank:], positions, dims, 30.0)
+        for t in range(n):
+            page, at = table[token_seq[t], positions[t] // 64], positions[t] % 64
+            got = host(pool[page, at])
+            assert rel(got[:rank], want_c[t]) < tol and rel(got[rank:], want_r[t]) < tol
+            written[page, at] = True
+    assert bool((pool[~written] == 5.0).all())
+
+
+@pytest.mark.parametrize("dtype, tol", DTYPES)
+@pytest.mark.parametrize("splits", [1, 5, 40])
+def test_fused_steps_after_the_attention_of_few_tokens(dtype, tol, splits):
+    """One launch: the splits' partial results joined (or the single result read), times W_uv per head, times the gate."""
+    rng = np.random.default_rng(13)
+    n, heads, rank, vdim = 4, 3, 40, 24
+    uv = dev(rng.standard_normal((heads, rank, vdim)) / np.sqrt(rank), dtype)
+    gate_rows = dev(rng.standard_normal((n, heads * vdim + 6)), dtype)
+    out = torch.zeros((n + 1, heads * vdim), dtype=dtype, device=DEV)
+    if splits == 1:
+        mixed_latent = dev(rng.standard_normal((n, heads * rank)), dtype)
+        merged = host(mixed_latent).reshape(n, heads, rank)
+        kernels.latent_decode_finish(uv, out, n_tokens=n, n_splits=1, mixed_latent=mixed_latent, gate=gate_rows[:, 6:])
+    else:
+        sums = rng.standard_normal((n, heads, splits, rank))
+        maxima = rng.standard_normal((n, heads, splits)) * 3.0
+        maxima[:, :, 1] = -np.inf                       # a split that saw no key
+        sums[:, :, 1] = 0.0
+        denoms = rng.uniform(0.5, 2.0, (n, heads, splits))
+        denoms[:, :, 1] = 0.0
+        part = np.concatenate([sums, maxima[..., None], denoms[..., None]], axis=-1)
+        w = np.where(np.isfinite(maxima), np.exp(maxima - maxima.max(axis=-1, keepdims=True)), 0.0)
+        merged = (sums * w[..., None]).sum(axis=2) / (denoms * w).sum(axis=2)[..., None]
+        kernels.latent_decode_finish(uv, out, n_tokens=n, n_splits=splits, scratch=dev(part.reshape(-1)),
+                                     gate=gate_rows[:, 6:])
+    want = np.einsum("thr,hrv->thv", merged, host(uv)) * plain.sigmoid(host(gate_rows[:, 6:]).reshape(n, heads, vdim))
+    assert rel(host(out[:n]).reshape(n, heads, vdim), want) < tol and bool((out[n:] == 0).all())
