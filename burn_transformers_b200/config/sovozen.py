@@ -10,7 +10,9 @@ config.json gives every size and constant:
                  "mlp": {"kind": "dense", "ff": F} | null},
                 {"type": "lightning", "mixer": {"heads", "dim", "vdim", "decay": [one per head]}, "mlp": ...}]}
 
-Nothing has a default: a key that is missing is an error that names it.
+Sizes have no defaults: a size that is missing is an error that names it.  What a configuration does not mention does
+not exist: a layer without an `mlp` key has no feed-forward, a missing `embedding.scale` or `logit_scale` is 1, and a
+mixer without rotated channels (`rot_dim` 0) needs no `rot`.
 """
 from __future__ import annotations
 
@@ -43,7 +45,7 @@ class SovozenConfig(ModelConfig):
     width: int = dataclasses.field(default=0, metadata={"aliases": ()})
     embedding: dict = dataclasses.field(default_factory=dict, metadata={"aliases": ()})
     norm: dict = dataclasses.field(default_factory=dict, metadata={"aliases": ()})
-    logit_scale: float = dataclasses.field(default=float("nan"), metadata={"aliases": ()})
+    logit_scale: float = dataclasses.field(default=1.0, metadata={"aliases": ()})
     layers: list = dataclasses.field(default_factory=list, metadata={"aliases": ()})
 
     @property
@@ -52,7 +54,7 @@ class SovozenConfig(ModelConfig):
 
     @property
     def embedding_scale(self) -> float:
-        return float(self.embedding["scale"])
+        return float(self.embedding.get("scale", 1.0))
 
     @property
     def eps(self) -> float:
@@ -78,7 +80,10 @@ class SovozenConfig(ModelConfig):
     def validate(self) -> None:
         self._check_model_type(self.architecture)
         self._check_extents(("vocab", "width"))
-        self._number("embedding", self.embedding, "scale")
+        if not isinstance(self.embedding, dict):
+            self._fail("embedding", "must be an object")
+        if "scale" in self.embedding:
+            self._number("embedding", self.embedding, "scale")
         self._number("norm", self.norm, "eps", positive=True)
         if not _is_number(self.logit_scale):
             self._fail("logit_scale", f"expected a finite number, found {self.logit_scale!r}")
@@ -99,9 +104,7 @@ class SovozenConfig(ModelConfig):
                 decay = mixer.get("decay")
                 if not isinstance(decay, list) or len(decay) != mixer["heads"] or not all(_is_number(d) for d in decay):
                     self._fail(f"{where}.mixer.decay", f"expected one number per head ({mixer['heads']})")
-            if "mlp" not in layer:
-                self._fail(f"{where}.mlp", "is missing (null for a layer without a feed-forward)")
-            mlp = layer["mlp"]
+            mlp = layer.get("mlp")
             if mlp is not None:
                 if not isinstance(mlp, dict) or mlp.get("kind") not in FEED_FORWARD_KINDS:
                     self._fail(f"{where}.mlp.kind", f"expected one of {list(FEED_FORWARD_KINDS)}")
@@ -112,6 +115,8 @@ class SovozenConfig(ModelConfig):
         self._ints(where, mixer, ("rot_dim",), minimum=0)
         self._number(where, mixer, "scale")
         rot = mixer.get("rot")
+        if rot is None and mixer["rot_dim"] == 0:
+            rot = {"dims": 0, "base": 1.0}
         if not isinstance(rot, dict):
             self._fail(f"{where}.rot", "is missing")
         self._ints(f"{where}.rot", rot, ("dims",), minimum=0)

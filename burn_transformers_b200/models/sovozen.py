@@ -37,7 +37,8 @@ def build_sovozen(config: SovozenConfig) -> ModelPlan:
         reads = None
         if layer["type"] == "latent_attention":
             reads = m.get("kv_from")
-            rotary = InterleavedRotary(m["rot"]["dims"], m["rot"]["base"])
+            rot = m.get("rot") or {"dims": 0, "base": 1.0}
+            rotary = InterleavedRotary(rot["dims"], rot["base"])
             out_std = (m["heads"] * m["vdim"]) ** -0.5
             mixer = LatentAttention(width, m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["scale"], eps,
                                     rotary, owns_latent=reads is None, sink=True, init_std=std, out_init_std=out_std)
@@ -57,7 +58,7 @@ def build_sovozen(config: SovozenConfig) -> ModelPlan:
         names[p + "mix.in"] = (mixer, "in.weight")
         sources[p + "mix.in"] = Concat(tuple(Stored(name) for name, _ in stacked), 0, tuple(size for _, size in stacked))
         norm2 = feed_forward = None
-        if layer["mlp"] is not None:
+        if layer.get("mlp") is not None:
             inner = layer["mlp"]["ff"]
             norm2 = LayerNorm(width, eps, bias=False)
             feed_forward = GatedFeedForward(width, inner, "gelu_new", init_std=std, down_init_std=inner ** -0.5)

@@ -61,12 +61,18 @@ def sink_softmax_mix(scores, sink, values):
     return (e / denom) @ values
 
 
+def rotation_of(m):
+    """(dims, base) of a mixer's rotation; a mixer without rotated channels may leave it out."""
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    return rot["dims"], rot["base"]
+
+
 def latent_keys(h, m, w, prefix, eps, positions):
     """The latent c [T, kv_rank] and the rotated shared key part [T, rot_dim] of a layer that owns a W_dkv."""
     rank, rot_dim = m["kv_rank"], m["rot_dim"]
     down = h @ w[prefix + "dkv"].T
     c = rms_norm(down[:, :rank], w[prefix + "dkv.norm"], eps)
-    k_rot = rotate_interleaved(down[:, rank:rank + rot_dim], positions, m["rot"]["dims"], m["rot"]["base"])
+    k_rot = rotate_interleaved(down[:, rank:rank + rot_dim], positions, *rotation_of(m))
     return c, k_rot
 
 
@@ -76,7 +82,7 @@ def latent_attention(h, m, w, prefix, eps, positions, c, k_rot):
     H, dim, rot_dim, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     q = (h @ w[prefix + "q"].T).reshape(T, H, dim + rot_dim)
     q_plain = q[:, :, :dim]
-    q_rot = rotate_interleaved(q[:, :, dim:], positions, m["rot"]["dims"], m["rot"]["base"])
+    q_rot = rotate_interleaved(q[:, :, dim:], positions, *rotation_of(m))
     k_plain = (c @ w[prefix + "uk"].T).reshape(T, H, dim)
     v = (c @ w[prefix + "uv"].T).reshape(T, H, vdim)
     causal = np.tril(np.ones((T, T), dtype=bool))
@@ -114,7 +120,7 @@ def forward(config, w, tokens, *, return_layers=False):
     """Logits [T, vocab] of one sequence; with `return_layers` also the residual stream after every layer."""
     eps = config["norm"]["eps"]
     positions = np.arange(len(tokens))
-    x = w["embed"][np.asarray(tokens)] * config["embedding"]["scale"]
+    x = w["embed"][np.asarray(tokens)] * config.get("embedding", {}).get("scale", 1.0)
     latents = {}
     after = []
     for i, layer in enumerate(config["layers"]):
@@ -135,5 +141,5 @@ def forward(config, w, tokens, *, return_layers=False):
         if layer.get("mlp") is not None:
             x = x + dense_feed_forward(layer_norm(x, w[f"l{i}.norm2"], eps), w, f"l{i}.mlp.")
         after.append(x.copy())
-    logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T * config["logit_scale"]
+    logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T * config.get("logit_scale", 1.0)
     return (logits, np.stack(after)) if return_layers else logits

@@ -44,13 +44,28 @@ def broken(change):
     (lambda d: d["layers"][3]["mixer"].update(kv_from=1), "layers[3].mixer.kv_from"),      # a recurrence has no latent
     (lambda d: d["layers"][5]["mixer"].update(kv_from=3), "layers[5].mixer.kv_from"),      # a reader has none of its own
     (lambda d: d["layers"][3]["mixer"].update(kv_rank=40), "layers[3].mixer.kv_from"),     # sizes must agree
-    (lambda d: d["layers"][2].pop("mlp"), "layers[2].mlp"),
     (lambda d: d["layers"][2]["mlp"].update(kind="moe"), "layers[2].mlp.kind"),
 ])
 def test_a_broken_configuration_names_its_field(change, field):
     with pytest.raises(ConfigError) as error:
         SovozenConfig.from_dict(broken(change))
     assert f"sovozen.{field}" in str(error.value)
+
+
+def test_what_a_configuration_does_not_mention_does_not_exist():
+    data = copy.deepcopy(sc.SMALL)
+    data["layers"][2].pop("mlp")
+    data.pop("logit_scale")
+    data["embedding"].pop("scale")
+    data["layers"][2]["mixer"].update(rot_dim=0)
+    data["layers"][2]["mixer"].pop("rot")
+    data["layers"][5]["mixer"].update(rot_dim=0)
+    data["layers"][5]["mixer"].pop("rot")
+    config = SovozenConfig.from_dict(data)
+    assert config.logit_scale == 1.0 and config.embedding_scale == 1.0
+    plan = architecture_for("Sovozen").build(config)
+    assert plan.blocks[2].feed_forward is None and plan.blocks[2].mixer.rot_dim == 0
+    assert "l2.norm2" not in plan.weights.stored() and plan.cache_needs()[2].kv.head_dim == 40
 
 
 def test_the_plan_follows_the_layer_list():

@@ -149,6 +149,25 @@ def test_sharp_softmaxes_find_single_far_keys(name, tmp_path):
         assert err < 3e-4, f"{err:.3e} at {where}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_configuration_that_leaves_out_what_it_does_not_have(tmp_path, dtype):
+    """No `mlp` key, no scales, a latent layer without rotated channels and without a `rot` entry, read by a later layer."""
+    config = {"architecture": "Sovozen", "vocab": 90, "width": 40, "embedding": {}, "norm": {"eps": 1e-5},
+              "layers": [{"type": "latent_attention", "mixer": {"heads": 2, "dim": 12, "rot_dim": 0, "vdim": 20, "kv_rank": 16,
+                                                               "scale": 0.3}},
+                         sc.lightning(1, 8, 12, [0.9], ff=48),
+                         {"type": "latent_attention", "mixer": {"heads": 3, "dim": 8, "rot_dim": 0, "vdim": 8, "kv_rank": 16,
+                                                               "scale": 0.2, "kv_from": 0}, "mlp": None}]}
+    folder = sc.make_folder(tmp_path, config, seed=3)
+    pcfg, pw = sc.load_plain(folder)
+    seqs = sc.prompts(config, [1, 70, 33], seed=3)
+    ref = [plain.forward(pcfg, pw, s) for s in seqs]
+    engine = engine_for(folder, dtype)
+    for got in (replay.whole(engine, seqs), replay.tail_one_by_one(engine, seqs, tail=10)):
+        err, where = replay.worst_error(got, ref)
+        assert err < TOL[dtype], f"{err:.3e} at {where}"
+
+
 def plain_greedy(pcfg, pw, prompt, n):
     seq = list(prompt)
     margins = []
