@@ -136,12 +136,24 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
 }
 
-enum Activation : int { kActNone = 0, kActGeluTanh = 1, kActGeluErf = 2 };
+// kActSwishClamp is a rule for a (gate, up) pair, see gated_pair; alone it leaves a value as it is.
+enum Activation : int { kActNone = 0, kActGeluTanh = 1, kActGeluErf = 2, kActSwishClamp = 3 };
 
 __device__ __forceinline__ float apply_activation(float v, int act) {
   if (act == kActGeluTanh) return gelu_tanh(v);
   if (act == kActGeluErf) return gelu_erf(v);
   return v;
+}
+
+// The hidden value of a gated feed-forward from its pair (gate g, up u): act(g) * u, or, for kActSwishClamp,
+// g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and u' = u clamped to [-limit, limit].
+__device__ __forceinline__ float gated_pair(float g, float u, int act, float limit) {
+  if (act == kActSwishClamp) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return apply_activation(g, act) * u;
 }
 
 // Where the keys and values of one attention call live.

@@ -1,0 +1,436 @@
+// Routed experts: the router with its choice of experts, the sorting of (token, choice) pairs by expert, the experts'
+// two products over the sorted rows, and the weighted sum back into the stream.
+//
+//   moe_route    per token: z = W_r x in 32-bit, s = sigmoid(z); experts lie in `n_groups` equal groups of neighbours, a
+//                group's score is the sum of its two largest s, only the `keep` best groups may give experts; the `top`
+//                largest s among those are chosen (equal scores: the lower index); weights s / (sum of the chosen + 1e-20)
+//                * scale.
+//   moe_sort     counts the pairs per expert, gives each pair a row in expert order, and numbers the row tiles
+//                (tiles never straddle two experts).
+//   moe_expert_in   hidden[r] = pair rule(gate_e x, up_e x) for the rows of expert e (x gathered by the pair's token)
+//   moe_expert_out  part[r] = weight(r) * down_e hidden[r]   (32-bit)
+//   moe_combine  stream[t] += sum over the token's pairs, in the order of its choices: no atomics, a fixed order.
+//
+// The products exist as 32-bit multiply-adds (float32, and every shape) and on tensor cores (bfloat16, mma.sync
+// m16n8k16 with 32-bit accumulators, K a multiple of 16).  A row's result never depends on its neighbours in the tile.
+#include "common.cuh"
+
+namespace bt {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ router, int n_tokens, int K, int E,
+                 int top, int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* score = sm + (size_t)warp * 3 * E;   // [E] sigmoid scores
+  float* cand = score + E;                    // [E] scores still to choose from (-1: not allowed, -2: taken)
+  float* group = cand + E;                    // [n_groups] group scores
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
+  const T* row = x + (long long)t * x_row_stride;
+  for (int e = 0; e < E; ++e) {
+    const T* w = router + (long long)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_float(row[k]), to_float(w[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) score[e] = 1.f / (1.f + expf(-acc));
+  }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) cand[e] = score[e];
+  if (keep < n_groups) {
+    const int size = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -1.f, b = -1.f;               // the two largest of the group
+      for (int e = g * size; e < (g + 1) * size; ++e) {
+        const float s = score[e];
+        if (s > a) { b = a; a = s; } else if (s > b) { b = s; }
+      }
+      group[g] = a + (b >= 0.f ? b : 0.f);
+    }
+    __syncwarp();
+    // take `keep` groups out (marking them), then close the experts of the groups that stayed
+    for (int r = 0; r < keep; ++r) {
+      float v = -INFINITY;
+      int i = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (group[g] > v) { v = group[g]; i = g; }
+      warp_argmax(v, i);
+      __syncwarp();
+      if (lane == 0) group[i] = -INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (group[e / size] != -INFINITY) cand[e] = -1.f;
+  }
+  __syncwarp();
+  float sum = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float v = -INFINITY;
+    int i = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (cand[e] > v) { v = cand[e]; i = e; }
+    warp_argmax(v, i);
+    __syncwarp();
+    if (lane == 0) {
+      cand[i] = -2.f;
+      ids[(long long)t * top + r] = i;
+      weights[(long long)t * top + r] = v;
+    }
+    sum += v;
+    __syncwarp();
+  }
+  if (lane < top) {
+    const long long at = (long long)t * top + lane;
+    weights[at] = weights[at] / (sum + 1e-20f) * scale;
+  }
+}
+
+// One block.  offsets[e]: first sorted row of expert e (offsets[E] = all rows); tile_first[e]: first row tile of expert e
+// (tile_first[E] = all tiles); order[r]: the pair (token * top + choice) that lies in sorted row r; place[pair]: its row.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int total, int E, int tile_rows, int* __restrict__ offsets,
+                int* __restrict__ tile_first, int* __restrict__ order, int* __restrict__ place) {
+  extern __shared__ int ism[];
+  int* count = ism;         // [E]
+  int* cursor = ism + E;    // [E]
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < total; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = rows;
+      tile_first[e] = tiles;
+      cursor[e] = rows;
+      rows += count[e];
+      tiles += (count[e] + tile_rows - 1) / tile_rows;
+    }
+    offsets[E] = rows;
+    tile_first[E] = tiles;
+  }
+  __syncthreads();
+  // lanes of a warp that hold the same expert take consecutive rows from one atomic; which pair gets which of an
+  // expert's rows does not matter: a row's result does not depend on its place
+  for (int base = 0; base < total; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    if (i < total) {
+      const int e = ids[i];
+      const unsigned same = __match_any_sync(__activemask(), e);
+      const int rank = __popc(same & ((1u << (threadIdx.x & 31)) - 1));
+      int first = 0;
+      if (rank == 0) first = atomicAdd(&cursor[e], __popc(same));
+      first = __shfl_sync(same, first, __ffs(same) - 1);
+      order[first + rank] = i;
+      place[i] = first + rank;
+    }
+  }
+}
+
+// Which expert and which of its rows a row tile holds: the last e with tile_first[e] <= tile.
+__device__ __forceinline__ bool moe_tile(const int* __restrict__ offsets, const int* __restrict__ tile_first, int E,
+                                         int tile, int tile_rows, int& expert, int& row0, int& rows) {
+  if (tile >= tile_first[E]) return false;
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (tile_first[mid] <= tile) lo = mid; else hi = mid - 1;
+  }
+  expert = lo;
+  row0 = offsets[lo] + (tile - tile_first[lo]) * tile_rows;
+  rows = min(tile_rows, offsets[lo + 1] - row0);
+  return true;
+}
+
+// ---- the products as 32-bit multiply-adds ---------------------------------------------------------------------------
+constexpr int MS_BM = 32, MS_BN = 64, MS_BK = 32;
+
+struct MoeArgs {
+  const int* offsets;
+  const int* tile_first;
+  const int* order;
+  const float* pair_weight;   // [pairs] (second product)
+  int E, top, K, N, act;
+  float limit;
+  long long a_row_stride;
+};
+
+// IN: hidden[r, j] = pair(gate_e[j] . x, up_e[j] . x), w: [E][2N][K];  else part[r, c] = weight * (down_e[c] . hidden[r]),
+// w: [E][N][K].
+template <typename T, bool IN>
+__global__ void __launch_bounds__(256)
+moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out, MoeArgs p) {
+  __shared__ float a_s[MS_BK][MS_BM + 1];
+  __shared__ float w_s[IN ? 2 : 1][MS_BK][MS_BN + 1];
+  __shared__ int src_row[MS_BM];
+  pdl_trigger();
+  pdl_wait();
+  int expert, row0, rows;
+  if (!moe_tile(p.offsets, p.tile_first, p.E, blockIdx.y, MS_BM, expert, row0, rows)) return;
+  const int n0 = blockIdx.x * MS_BN;
+  if (threadIdx.x < MS_BM) {
+    const int r = row0 + threadIdx.x;
+    src_row[threadIdx.x] = threadIdx.x < rows ? (IN ? p.order[r] / p.top : r) : -1;
+  }
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 4 columns, 2 rows a thread
+  float acc[IN ? 2 : 1][2][4] = {};
+  const T* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
+  for (int k0 = 0; k0 < p.K; k0 += MS_BK) {
+    for (int i = threadIdx.x; i < MS_BM * MS_BK; i += 256) {
+      const int r = i / MS_BK, k = i - r * MS_BK;
+      const int src = src_row[r];
+      a_s[k][r] = src >= 0 && k0 + k < p.K ? to_float(a[(long long)src * p.a_row_stride + k0 + k]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < MS_BN * MS_BK; i += 256) {
+      const int n = i / MS_BK, k = i - n * MS_BK;
+      const bool in = n0 + n < p.N && k0 + k < p.K;
+      w_s[0][k][n] = in ? to_float(w_e[(long long)(n0 + n) * p.K + k0 + k]) : 0.f;
+      if (IN) w_s[1][k][n] = in ? to_float(w_e[(long long)(p.N + n0 + n) * p.K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < MS_BK; ++k) {
+      const float a0 = a_s[k][ty * 2], a1 = a_s[k][ty * 2 + 1];
+#pragma unroll
+      for (int h = 0; h < (IN ? 2 : 1); ++h)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float b = w_s[h][k][tx * 4 + c];
+          acc[h][0][c] = fmaf(a0, b, acc[h][0][c]);
+          acc[h][1][c] = fmaf(a1, b, acc[h][1][c]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rl = ty * 2 + i;
+    if (rl >= rows) continue;
+    const long long r = row0 + rl;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int n = n0 + tx * 4 + c;
+      if (n >= p.N) continue;
+      if (IN)
+        reinterpret_cast<T*>(out)[r * p.N + n] = from_float<T>(gated_pair(acc[0][i][c], acc[IN ? 1 : 0][i][c], p.act, p.limit));
+      else
+        reinterpret_cast<float*>(out)[r * p.N + n] = acc[0][i][c] * p.pair_weight[p.order[r]];
+    }
+  }
+}
+
+// ---- the products on tensor cores (bfloat16) -----------------------------------------------------------------------
+// A block: 32 rows x 64 columns (both halves of the pair for the first product), 4 warps, each 32 rows x 16 columns; K in
+// pieces of 32 through shared memory (rows padded to 40 elements: fragment loads fall into different banks).
+constexpr int MM_BM = 32, MM_BN = 64, MM_BK = 32, MM_LD = MM_BK + 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <bool IN>
+__global__ void __launch_bounds__(128)
+moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                      MoeArgs p) {
+  __shared__ __align__(16) __nv_bfloat16 a_s[MM_BM][MM_LD];
+  __shared__ __align__(16) __nv_bfloat16 w_s[IN ? 2 : 1][MM_BN][MM_LD];
+  __shared__ int src_row[MM_BM];
+  pdl_trigger();
+  pdl_wait();
+  int expert, row0, rows;
+  if (!moe_tile(p.offsets, p.tile_first, p.E, blockIdx.y, MM_BM, expert, row0, rows)) return;
+  const int n0 = blockIdx.x * MM_BN;
+  if (threadIdx.x < MM_BM) {
+    const int r = row0 + threadIdx.x;
+    src_row[threadIdx.x] = threadIdx.x < rows ? (IN ? p.order[r] / p.top : r) : -1;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  float acc[IN ? 2 : 1][2][2][4] = {};      // [half][m tile][n tile][fragment]
+  const __nv_bfloat16* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < p.K; k0 += MM_BK) {
+    // 16-byte pieces: 4 a row
+    for (int i = threadIdx.x; i < MM_BM * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      const int src = src_row[r];
+      uint4 v = zero;
+      if (src >= 0 && k0 + c < p.K) v = *reinterpret_cast<const uint4*>(a + (long long)src * p.a_row_stride + k0 + c);
+      *reinterpret_cast<uint4*>(&a_s[r][c]) = v;
+    }
+    for (int i = threadIdx.x; i < MM_BN * 4; i += 128) {
+      const int n = i >> 2, c = (i & 3) * 8;
+      const bool in = n0 + n < p.N && k0 + c < p.K;
+      *reinterpret_cast<uint4*>(&w_s[0][n][c]) =
+          in ? *reinterpret_cast<const uint4*>(w_e + (long long)(n0 + n) * p.K + k0 + c) : zero;
+      if (IN)
+        *reinterpret_cast<uint4*>(&w_s[IN ? 1 : 0][n][c]) =
+            in ? *reinterpret_cast<const uint4*>(w_e + (long long)(p.N + n0 + n) * p.K + k0 + c) : zero;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MM_BK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const __nv_bfloat16* base = &a_s[mt * 16 + gid][kk + tig * 2];
+        af[mt][0] = *reinterpret_cast<const uint32_t*>(base);
+        af[mt][1] = *reinterpret_cast<const uint32_t*>(base + 8 * MM_LD);
+        af[mt][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+        af[mt][3] = *reinterpret_cast<const uint32_t*>(base + 8 * MM_LD + 8);
+      }
+#pragma unroll
+      for (int h = 0; h < (IN ? 2 : 1); ++h)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const __nv_bfloat16* base = &w_s[h][warp * 16 + nt * 8 + gid][kk + tig * 2];
+          uint32_t bf[2];
+          bf[0] = *reinterpret_cast<const uint32_t*>(base);
+          bf[1] = *reinterpret_cast<const uint32_t*>(base + 8);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) mma_bf16_16816(acc[h][mt][nt], af[mt], bf);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int rl = mt * 16 + gid + half * 8;
+      if (rl >= rows) continue;
+      const long long r = row0 + rl;
+      const float scale = IN ? 1.f : p.pair_weight[p.order[r]];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + warp * 16 + nt * 8 + tig * 2 + c;
+          if (n >= p.N) continue;
+          const float v = acc[0][mt][nt][half * 2 + c];
+          if (IN)
+            reinterpret_cast<__nv_bfloat16*>(out)[r * p.N + n] =
+                __float2bfloat16_rn(gated_pair(v, acc[IN ? 1 : 0][mt][nt][half * 2 + c], p.act, p.limit));
+          else
+            reinterpret_cast<float*>(out)[r * p.N + n] = v * scale;
+        }
+    }
+}
+
+// stream[t, c] += sum_j part[place[t * top + j], c]
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place, float* __restrict__ stream,
+                   long long n_tokens, int top, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = n_tokens * width;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) sum += part[(long long)place[t * top + j] * width + c];
+    stream[i] += sum;
+  }
+}
+
+}  // namespace bt
+
+extern "C" int bt_moe_route(const void* x, long long x_row_stride, const void* router, int n_tokens, int K, int E, int top,
+                            int n_groups, int keep, float scale, int* ids, float* weights, int dtype,
+                            cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_tokens >= 0 && K > 0 && E > 0 && E <= 1024 && top > 0 && top <= 32 && n_groups > 0 && E % n_groups == 0 &&
+               keep > 0 && keep <= n_groups && top <= keep * (E / n_groups),
+           "moe_route: bad sizes experts=%d (up to 1024) top=%d (up to 32) groups=%d keep=%d", E, top, n_groups, keep);
+  if (n_tokens == 0) return 0;
+  const dim3 grid((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), block(ROUTE_WARPS * 32);
+  const size_t smem = (size_t)ROUTE_WARPS * 3 * E * sizeof(float);
+  if (dtype == kF32)
+    BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<float>, grid, block, smem, stream, 1, (const float*)x, x_row_stride,
+                                      (const float*)router, n_tokens, K, E, top, n_groups, keep, scale, ids, weights));
+  else if (dtype == kBF16)
+    BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream, 1,
+                                      (const __nv_bfloat16*)x, x_row_stride, (const __nv_bfloat16*)router, n_tokens, K, E,
+                                      top, n_groups, keep, scale, ids, weights));
+  else
+    return fail("moe_route: unknown dtype %d", dtype);
+  return 0;
+}
+
+extern "C" int bt_moe_tile_rows() { return bt::MS_BM; }
+
+extern "C" int bt_moe_sort(const int* ids, int total, int E, int* offsets, int* tile_first, int* order, int* place,
+                           cudaStream_t stream) {
+  using namespace bt;
+  static_assert(MS_BM == MM_BM, "both product kernels read the same row tiles");
+  BT_CHECK(total >= 0 && E > 0 && E <= 4096, "moe_sort: bad sizes pairs=%d experts=%d", total, E);
+  BT_PDL_OK("moe_sort", launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, 1, ids,
+                                   total, E, MS_BM, offsets, tile_first, order, place));
+  return 0;
+}
+
+// first: 1 = the experts' first product (a: the tokens' rows [tokens, K]; w: [E][2N][K]; out: [pairs, N] of the
+// compute type), 0 = the second (a: [pairs, K]; w: [E][N][K]; out: [pairs, N] 32-bit, times the pair's weight).
+extern "C" int bt_moe_expert(int first, const void* a, long long a_row_stride, const void* w, void* out,
+                             const int* offsets, const int* tile_first, const int* order, const float* pair_weight,
+                             int pairs, int E, int top, int K, int N, int act, float limit, int tensor_cores, int dtype,
+                             cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(pairs >= 0 && E > 0 && top > 0 && K > 0 && N > 0, "moe_expert: bad sizes pairs=%d experts=%d K=%d N=%d", pairs,
+           E, K, N);
+  if (pairs == 0) return 0;
+  MoeArgs p;
+  p.offsets = offsets; p.tile_first = tile_first; p.order = order; p.pair_weight = pair_weight;
+  p.E = E; p.top = top; p.K = K; p.N = N; p.act = act; p.limit = limit; p.a_row_stride = a_row_stride;
+  const int tiles = (pairs + MS_BM - 1) / MS_BM + E;      // no more row tiles than this, however the pairs fall
+  BT_CHECK(tiles <= 65535, "moe_expert: %d pairs are more row tiles than a launch takes", pairs);
+  const dim3 grid((N + MS_BN - 1) / MS_BN, tiles);
+  if (dtype == kBF16 && tensor_cores && K % 8 == 0 && a_row_stride % 8 == 0 && (unsigned long long)a % 16 == 0 &&
+      (unsigned long long)w % 16 == 0) {
+    if (first)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<true>, grid, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    else
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_mma_kernel<false>, grid, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    return 0;
+  }
+#define BT_MOE(T, FIRST) \
+  BT_PDL_OK("moe_expert", launch_pdl(moe_expert_simt_kernel<T, FIRST>, grid, dim3(256), 0, stream, 1, (const T*)a, (const T*)w, out, p))
+  if (dtype == kF32) { if (first) BT_MOE(float, true); else BT_MOE(float, false); }
+  else if (dtype == kBF16) { if (first) BT_MOE(__nv_bfloat16, true); else BT_MOE(__nv_bfloat16, false); }
+  else return fail("moe_expert: unknown dtype %d", dtype);
+#undef BT_MOE
+  return 0;
+}
+
+extern "C" int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top,
+                              int width, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_tokens >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  if (n_tokens == 0) return 0;
+  const long long total = n_tokens * width;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  BT_PDL_OK("moe_combine", launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, stream, 1, part, place, stream_rows,
+                                      n_tokens, top, width));
+  return 0;
+}

@@ -5,16 +5,21 @@
 namespace bt {
 
 // out[r, c] = x[r, c] / sqrt(mean_c(x[r]^2) + eps) * weight[c]  (* sigmoid(gate[r, c]) if gate)
+// With `groups` > 1 a row is `groups` runs of `width` channels, each normed by its own root mean square (heads side by
+// side); weight and gate go on over all channels of the row.
 template <typename TIn, typename TGate, typename TOut>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* __restrict__ weight,
                const TGate* __restrict__ gate, long long gate_row_stride, TOut* __restrict__ out,
-               long long out_row_stride, int width, float eps) {
+               long long out_row_stride, int width, int groups, float eps) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
-  const int r = blockIdx.x;
-  const TIn* src = x + (long long)r * x_row_stride;
+  const int r = blockIdx.x / groups, first = (blockIdx.x - r * groups) * width;
+  const TIn* src = x + (long long)r * x_row_stride + first;
+  weight += first;
+  if (gate) gate += first;
+  out += first;
   float ss = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float v = to_float(src[c]);
@@ -56,10 +61,11 @@ rotary_interleaved_kernel(const T* src, long long src_row_stride, int src_vec_st
   }
 }
 
-// out[r, j] = act(x[r, j]) * x[r, inner + j]
+// out[r, j] = act(x[r, j]) * x[r, inner + j]  (or the clamped pair rule of common.cuh: gated_pair)
 template <typename T>
 __global__ void __launch_bounds__(256)
-gated_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long n_rows, int inner, int act) {
+gated_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long n_rows, int inner, int act,
+                        float limit) {
   pdl_trigger();
   pdl_wait();
   const long long total = n_rows * inner;
@@ -67,14 +73,14 @@ gated_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long 
     const long long r = i / inner;
     const int j = (int)(i - r * inner);
     const float g = to_float(x[r * 2 * inner + j]), u = to_float(x[r * 2 * inner + inner + j]);
-    out[i] = from_float<T>(apply_activation(g, act) * u);
+    out[i] = from_float<T>(gated_pair(g, u, act, limit));
   }
 }
 
 // The same for bfloat16 rows whose halves are whole 16-byte pieces: a thread takes 8 channels at a time.
 __global__ void __launch_bounds__(256)
 gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, long long n_rows,
-                               int inner, int act) {
+                               int inner, int act, float limit) {
   pdl_trigger();
   pdl_wait();
   const int pieces = inner / 8;
@@ -91,7 +97,7 @@ gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-      o2[e] = __floats2bfloat162_rn(apply_activation(g.x, act) * u.x, apply_activation(g.y, act) * u.y);
+      o2[e] = __floats2bfloat162_rn(gated_pair(g.x, u.x, act, limit), gated_pair(g.y, u.y, act, limit));
     }
     *reinterpret_cast<uint4*>(out + r * inner + j) = ov;
   }
@@ -104,16 +110,29 @@ __global__ void __launch_bounds__(256) scale_kernel(float* __restrict__ x, long 
     x[i] *= scale;
 }
 
+// x[r, c] += vec[c]: one learned vector added to every row of the 32-bit stream
+__global__ void __launch_bounds__(256)
+add_vector_kernel(float* __restrict__ x, const float* __restrict__ vec, long long n_rows, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = n_rows * width;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    x[i] += vec[i % width];
+}
+
 template <typename TIn, typename TGate>
 static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGate* gate, long long gs, void* out,
-                          long long os, int n_rows, int width, float eps, int out_dtype, cudaStream_t stream) {
-  const int threads = width >= 1024 ? 256 : 128;
+                          long long os, int n_rows, int width, int groups, float eps, int out_dtype,
+                          cudaStream_t stream) {
+  width /= groups;
+  const int threads = width >= 1024 ? 256 : (width > 64 ? 128 : 64);
+  const dim3 grid((unsigned)n_rows * groups);
   if (out_dtype == kF32)
-    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, float>, dim3(n_rows), dim3(threads), 0, stream, 1, x, xs, w,
-                                    gate, gs, (float*)out, os, width, eps));
+    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, float>, grid, dim3(threads), 0, stream, 1, x, xs, w,
+                                    gate, gs, (float*)out, os, width, groups, eps));
   else
-    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, __nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 1, x,
-                                    xs, w, gate, gs, (__nv_bfloat16*)out, os, width, eps));
+    BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, __nv_bfloat16>, grid, dim3(threads), 0, stream, 1, x,
+                                    xs, w, gate, gs, (__nv_bfloat16*)out, os, width, groups, eps));
   return 0;
 }
 
@@ -121,24 +140,25 @@ static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGat
 
 extern "C" int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate,
                           int gate_dtype, long long gate_row_stride, void* out, int out_dtype, long long out_row_stride,
-                          int n_rows, int width, float eps, cudaStream_t stream) {
+                          int n_rows, int width, int groups, float eps, cudaStream_t stream) {
   using namespace bt;
-  BT_CHECK(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
+  BT_CHECK(n_rows >= 0 && width > 0 && groups > 0 && width % groups == 0 && (long long)n_rows * groups < (1ll << 31),
+           "rmsnorm: bad sizes rows=%d width=%d groups=%d", n_rows, width, groups);
   BT_CHECK((x_dtype == kF32 || x_dtype == kBF16) && (out_dtype == kF32 || out_dtype == kBF16) &&
            (gate == nullptr || gate_dtype == kF32 || gate_dtype == kBF16), "rmsnorm: unknown dtype");
   if (n_rows == 0) return 0;
   const bool gate_bf16 = gate != nullptr && gate_dtype == kBF16;
   if (x_dtype == kF32 && !gate_bf16)
     return launch_rmsnorm((const float*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out, out_row_stride,
-                          n_rows, width, eps, out_dtype, stream);
+                          n_rows, width, groups, eps, out_dtype, stream);
   if (x_dtype == kF32)
     return launch_rmsnorm((const float*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
-                          out_row_stride, n_rows, width, eps, out_dtype, stream);
+                          out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
   if (!gate_bf16)
     return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const float*)gate, gate_row_stride, out,
-                          out_row_stride, n_rows, width, eps, out_dtype, stream);
+                          out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
   return launch_rmsnorm((const __nv_bfloat16*)x, x_row_stride, weight, (const __nv_bfloat16*)gate, gate_row_stride, out,
-                        out_row_stride, n_rows, width, eps, out_dtype, stream);
+                        out_row_stride, n_rows, width, groups, eps, out_dtype, stream);
 }
 
 extern "C" int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
@@ -163,8 +183,8 @@ extern "C" int bt_rotary_interleaved(const void* src, long long src_row_stride, 
   return 0;
 }
 
-extern "C" int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, int dtype,
-                                   cudaStream_t stream) {
+extern "C" int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, float limit,
+                                   int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_rows >= 0 && inner > 0, "gated_activation: bad sizes rows=%lld inner=%d", n_rows, inner);
   if (n_rows == 0) return 0;
@@ -172,15 +192,15 @@ extern "C" int bt_gated_activation(const void* x, void* out, long long n_rows, i
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == kF32)
     BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1,
-                                             (const float*)x, (float*)out, n_rows, inner, act));
+                                             (const float*)x, (float*)out, n_rows, inner, act, limit));
   else if (dtype == kBF16 && inner % 8 == 0 && (unsigned long long)x % 16 == 0 && (unsigned long long)out % 16 == 0) {
     const long long pieces = total / 8;
     const int b8 = (int)((pieces + 255) / 256 < 148 * 16 ? (pieces + 255) / 256 : 148 * 16);
     BT_PDL_OK("gated_activation", launch_pdl(gated_activation_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, 1,
-                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act));
+                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act, limit));
   } else if (dtype == kBF16)
     BT_PDL_OK("gated_activation", launch_pdl(gated_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1,
-                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act));
+                                             (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n_rows, inner, act, limit));
   else
     return fail("gated_activation: unknown dtype %d", dtype);
   return 0;
@@ -191,5 +211,15 @@ extern "C" int bt_scale(float* x, long long n, float scale, cudaStream_t stream)
   if (n <= 0) return 0;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   BT_PDL_OK("scale", launch_pdl(scale_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, n, scale));
+  return 0;
+}
+
+extern "C" int bt_add_vector(float* x, const float* vec, long long n_rows, int width, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n_rows >= 0 && width > 0, "add_vector: bad sizes rows=%lld width=%d", n_rows, width);
+  if (n_rows == 0) return 0;
+  const long long total = n_rows * width;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  BT_PDL_OK("add_vector", launch_pdl(add_vector_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, vec, n_rows, width));
   return 0;
 }

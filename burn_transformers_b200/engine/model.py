@@ -25,10 +25,12 @@ class LayerCall:
 
     `cache` None: the call owns a cache entry of its own (so a block named twice keeps separate
     keys and values per call).  `cache` = index of an earlier call: this call reads that call's
-    entry and writes nothing.
+    entry and writes nothing.  `opens` = index of one of the plan's `stream_vectors`: that vector is added to the
+    residual stream right before this call (the first layer of a pass through a repeated run of layers).
     """
     block: int
     cache: int | None = None
+    opens: int | None = None
 
 
 @dataclasses.dataclass
@@ -51,9 +53,13 @@ class ModelPlan:
     # for a name of `names` whose tensor is not stored under that name and as the part uses it: how it is made from
     # the checkpoint's tensors (weights.spec.Stored / Split / Concat); the name is then only the model's own
     sources: dict = dataclasses.field(default_factory=dict)
+    # learned vectors that calls of the schedule add to the stream before they run (`LayerCall.opens`)
+    stream_vectors: Part | None = None
 
     def __post_init__(self):
         for index, call in enumerate(self.schedule):
+            if call.opens is not None and (self.stream_vectors is None or not 0 <= call.opens < self.stream_vectors.count):
+                raise ValueError(f"schedule[{index}] opens with vector {call.opens}, which the plan does not have")
             if not (0 <= call.block < len(self.blocks)):
                 raise ValueError(f"schedule[{index}] names block {call.block} of {len(self.blocks)}")
             if call.cache is not None:
@@ -77,6 +83,8 @@ class ModelPlan:
 
     def all_parts(self) -> list[Part]:
         found: list[Part] = [self.embedding, self.positions, self.final_norm, self.readout]
+        if self.stream_vectors is not None:
+            found.append(self.stream_vectors)
         for block in self.blocks:
             found.append(block)
             found.extend(block.parts().values())
@@ -100,6 +108,8 @@ class ModelPlan:
         self.embedding.forward(ctx, self.positions, residual)
         for index, call in enumerate(self.schedule):
             entry, owns = self.cache_entry(index)
+            if call.opens is not None:
+                self.stream_vectors.forward(ctx, residual, call.opens)
             self.blocks[call.block].forward(ctx, residual, entry, owns)
         if getattr(ctx, "side", None) is not None:
             ctx.side.join()       # (what parts ran beside the step must be done before the step's scratch is used again)

@@ -16,6 +16,8 @@ from .errors import KernelError, ShapeError
 _LIB = None
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu_tanh": 1, "gelu": 2, "gelu_erf": 2}
+# rules for the (gate, up) pair of a gated feed-forward: the activations above on the gate, or the clamped rule
+PAIR_RULES = dict(ACTIVATIONS, swish_clamp=3)
 PAGE_SIZE = 64
 
 
@@ -788,10 +790,13 @@ def lightning_scan(proj, q_off, k_off, v_off, state, slots, seq_start, decay, ou
                                        c_int(_code(proj.dtype)), _stream()))
 
 
-def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None):
+def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None, groups: int = 1):
     """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * weight  (* sigmoid(gate[r]) if `gate`), in 32-bit.  x, gate and out are
-    2-D views with contiguous channels (rows may lie further apart); 32-bit or bfloat16 each."""
+    2-D views with contiguous channels (rows may lie further apart); 32-bit or bfloat16 each.  With `groups` > 1 a row
+    is that many equal runs of channels (heads side by side), each divided by its own root mean square."""
     width = weight.shape[0]
+    if groups <= 0 or width % groups:
+        raise ShapeError(f"rmsnorm: {width} channels are no {groups} equal groups")
     _need(weight, "weight", torch.float32, (width,))
     for name, t in (("x", x), ("out", out)) + ((("gate", gate),) if gate is not None else ()):
         if t.dim() != 2 or t.shape[1] != width or t.stride(1) != 1 or not t.is_cuda or t.shape[0] < n_rows:
@@ -800,7 +805,8 @@ def rmsnorm(x, weight, out, eps: float, *, n_rows, gate=None):
     _check(library().bt_rmsnorm(_ptr(x), c_int(_code(x.dtype)), c_longlong(x.stride(0)), _ptr(weight), _ptr(gate),
                                 c_int(_code(gate.dtype)) if gate is not None else c_int(0),
                                 c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), c_int(_code(out.dtype)),
-                                c_longlong(out.stride(0)), c_int(n_rows), c_int(width), c_float(eps), _stream()))
+                                c_longlong(out.stride(0)), c_int(n_rows), c_int(width), c_int(groups), c_float(eps),
+                                _stream()))
 
 
 def rotary_interleaved(src, dst, positions, inv_freq, *, n_tokens, dims):
@@ -820,18 +826,120 @@ def rotary_interleaved(src, dst, positions, inv_freq, *, n_tokens, dims):
                                            c_int(length), c_int(dims), c_int(_code(src.dtype)), _stream()))
 
 
-def gated_activation(x, out, *, n_rows, activation):
-    """out[r, j] = act(x[r, j]) * x[r, inner + j] for x [rows, 2 * inner], in 32-bit, rounded once."""
+def gated_activation(x, out, *, n_rows, activation, limit: float = 0.0):
+    """out[r, j] = act(x[r, j]) * x[r, inner + j] for x [rows, 2 * inner], in 32-bit, rounded once.  `swish_clamp`:
+    g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = u clamped to [-limit, limit]."""
     inner = out.shape[1]
     _need(x, "x", (torch.float32, torch.bfloat16), (None, 2 * inner))
     _need(out, "out", x.dtype, (None, inner))
-    if activation not in ACTIVATIONS:
+    if activation not in PAIR_RULES:
         raise ShapeError(f"gated_activation: unknown activation {activation!r}")
     if x.shape[0] < n_rows or out.shape[0] < n_rows:
         raise ShapeError(f"gated_activation: {n_rows} rows asked of x[{x.shape[0]}] and out[{out.shape[0]}]")
     _work(0.0, 3.0 * n_rows * inner * x.element_size())
     _check(library().bt_gated_activation(_ptr(x), _ptr(out), c_longlong(n_rows), c_int(inner),
-                                         c_int(ACTIVATIONS[activation]), c_int(_code(x.dtype)), _stream()))
+                                         c_int(PAIR_RULES[activation]), c_float(limit), c_int(_code(x.dtype)), _stream()))
+
+
+def add_vector(x, vec, *, n_rows):
+    """x[r] += vec for the first `n_rows` rows of a contiguous 32-bit [rows, width] tensor; vec: 32-bit [width]."""
+    _need(x, "x", torch.float32, (None, vec.shape[0]))
+    _need(vec, "vec", torch.float32)
+    if x.shape[0] < n_rows:
+        raise ShapeError(f"add_vector: {n_rows} rows asked of x[{x.shape[0]}]")
+    _check(library().bt_add_vector(_ptr(x), _ptr(vec), c_longlong(n_rows), c_int(vec.shape[0]), _stream()))
+
+
+def mlstm_scan(proj, offsets, i_bias, f_bias, cap: float, q_scale: float, s, n, m, slots, seq_start, out, *, n_seqs,
+               n_heads, dim, vdim, max_new=None, scratch=None):
+    """The matrix memory's recurrence over the step's tokens of every sequence (csrc/mlstm.cu).  `offsets` = channels
+    of q, k, v (heads side by side) and of the input and forget gates (one channel a head) in the rows of `proj`.
+    s [slots, heads, dim, vdim], n [slots, heads, dim], m [slots, heads]: 32-bit state, read and written at
+    `slots[seq]`.  out [tokens, heads * vdim] 32-bit: S^T q / (max(|n . q|, exp(-m)) + 1e-6)."""
+    q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
+    _need(proj, "proj", (torch.float32, torch.bfloat16))
+    _need(s, "s", torch.float32, (None, n_heads, dim, vdim))
+    _need(n, "n", torch.float32, (s.shape[0], n_heads, dim))
+    _need(m, "m", torch.float32, (s.shape[0], n_heads))
+    _need(i_bias, "i_bias", torch.float32, (n_heads,))
+    _need(f_bias, "f_bias", torch.float32, (n_heads,))
+    _need(out, "out", torch.float32, (None, n_heads * vdim))
+    width = proj.shape[1]
+    if (max(q_off, k_off) + n_heads * dim > width or v_off + n_heads * vdim > width or max(i_off, f_off) + n_heads > width
+            or min(q_off, k_off, v_off, i_off, f_off) < 0):
+        raise ShapeError("mlstm_scan: the channel offsets leave the rows of proj")
+    n_rows = out.shape[0]
+    _work(4.0 * n_rows * n_heads * dim * vdim, n_rows * n_heads * ((2 * dim + vdim) * proj.element_size() + 4 * vdim)
+          + 8.0 * n_seqs * n_heads * dim * vdim)
+    _check(library().bt_mlstm_scan(_ptr(proj), c_longlong(width), c_int(q_off), c_int(k_off), c_int(v_off), c_int(i_off),
+                                   c_int(f_off), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale), _ptr(s),
+                                   _ptr(n), _ptr(m), _ptr(slots), _ptr(seq_start), _ptr(out), c_longlong(out.shape[1]),
+                                   c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), c_int(_code(proj.dtype)),
+                                   _stream()))
+
+
+def moe_route(x, router, ids, weights, *, n_tokens, top, n_groups=1, keep=1, scale=1.0):
+    """Per token the `top` experts with the largest sigmoid(router x) among the experts of the `keep` best of `n_groups`
+    groups of neighbours (a group's score: the sum of its two largest), and their weights score / (sum + 1e-20) * scale.
+    x [tokens, K] and router [experts, K] in the compute type, the products summed in 32-bit; ids int32 and weights
+    32-bit, [tokens, top]."""
+    e, k = router.shape
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, k))
+    _need(router, "router", x.dtype)
+    _need(ids, "ids", torch.int32, (None, top))
+    _need(weights, "weights", torch.float32, (None, top))
+    if min(x.shape[0], ids.shape[0], weights.shape[0]) < n_tokens:
+        raise ShapeError(f"moe_route: {n_tokens} tokens asked of shorter tensors")
+    _work(2.0 * n_tokens * e * k, n_tokens * k * x.element_size())
+    _check(library().bt_moe_route(_ptr(x), c_longlong(x.stride(0)), _ptr(router), c_int(n_tokens), c_int(k), c_int(e),
+                                  c_int(top), c_int(n_groups), c_int(keep), c_float(scale), _ptr(ids), _ptr(weights),
+                                  c_int(_code(x.dtype)), _stream()))
+
+
+def moe_sort(ids, offsets, tile_first, order, place, *, pairs, n_experts):
+    """Sorts the (token, choice) pairs by expert: offsets [experts + 1] first row of each expert, tile_first
+    [experts + 1] first row tile, order [pairs] the pair in each sorted row, place [pairs] the row of each pair."""
+    for name, t, count in (("ids", ids, pairs), ("offsets", offsets, n_experts + 1), ("tile_first", tile_first, n_experts + 1),
+                           ("order", order, pairs), ("place", place, pairs)):
+        _need(t, name, torch.int32)
+        if t.numel() < count:
+            raise ShapeError(f"moe_sort: {name} holds {t.numel()} integers, {count} are needed")
+    _check(library().bt_moe_sort(_ptr(ids), c_int(pairs), c_int(n_experts), _ptr(offsets), _ptr(tile_first), _ptr(order),
+                                 _ptr(place), _stream()))
+
+
+def moe_expert(first: bool, a, w, out, offsets, tile_first, order, pair_weight, *, pairs, top, activation=None,
+               limit: float = 0.0, tensor_cores: bool = True):
+    """One of the experts' two products over the sorted rows (csrc/moe.cu).  first: a [tokens, K] (gathered by the
+    pair's token), w [experts, 2 N, K] (gate rows, then up rows), out [pairs, N] = pair rule(gate, up).  second: a
+    [pairs, K], w [experts, N, K], out [pairs, N] 32-bit = the pair's weight times the product."""
+    e, rows_w, k = w.shape
+    n = rows_w // 2 if first else rows_w
+    _need(a, "a", (torch.float32, torch.bfloat16), (None, k))
+    _need(w, "w", a.dtype)
+    _need(out, "out", a.dtype if first else torch.float32, (None, n))
+    if out.shape[0] < pairs or (not first and a.shape[0] < pairs):
+        raise ShapeError(f"moe_expert: {pairs} rows asked of shorter tensors")
+    if activation not in PAIR_RULES:
+        raise ShapeError(f"moe_expert: unknown activation {activation!r}")
+    _work(2.0 * pairs * rows_w * k, w.numel() * w.element_size() + pairs * (k * a.element_size() + n * out.element_size()))
+    _check(library().bt_moe_expert(c_int(1 if first else 0), _ptr(a), c_longlong(a.stride(0)), _ptr(w), _ptr(out),
+                                   _ptr(offsets), _ptr(tile_first), _ptr(order), _ptr(pair_weight), c_int(pairs), c_int(e),
+                                   c_int(top), c_int(k), c_int(n), c_int(PAIR_RULES[activation]), c_float(limit),
+                                   c_int(1 if tensor_cores else 0), c_int(_code(a.dtype)), _stream()))
+
+
+def moe_combine(part, place, stream_rows, *, n_tokens, top):
+    """stream_rows[t] += sum over the token's `top` pairs of part[place[t * top + j]], in that order (32-bit)."""
+    width = stream_rows.shape[1]
+    _need(part, "part", torch.float32, (None, width))
+    _need(place, "place", torch.int32)
+    _need(stream_rows, "stream_rows", torch.float32)
+    if stream_rows.shape[0] < n_tokens or place.numel() < n_tokens * top:
+        raise ShapeError(f"moe_combine: {n_tokens} tokens asked of shorter tensors")
+    _work(0.0, 4.0 * n_tokens * width * (top + 2))
+    _check(library().bt_moe_combine(_ptr(part), _ptr(place), _ptr(stream_rows), c_longlong(n_tokens), c_int(top),
+                                    c_int(width), _stream()))
 
 
 def scale_(x, factor: float):

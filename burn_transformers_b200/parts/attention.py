@@ -37,7 +37,7 @@ class CausalSelfAttention(Mixer):
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, *,
                  causal: bool = True, window: int | None = None, bias: bool = True,
-                 init_std: float = 0.02, out_init_std: float | None = None, positions=None):
+                 init_std: float = 0.02, out_init_std: float | None = None, positions=None, out_scale: float = 1.0):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ShapeError(f"{n_heads} query heads cannot share {n_kv_heads} key heads")
         if not 1 <= head_dim <= self.MAX_HEAD_DIM:
@@ -53,6 +53,18 @@ class CausalSelfAttention(Mixer):
         self.proj_width = self.q_width + 2 * self.kv_width
         self.init_std = init_std
         self.out_init_std = init_std if out_init_std is None else out_init_std
+        # the mixer's result times this as it enters the residual stream: folded into the output projection when the
+        # weights are bound (in 32-bit, rounded once to the compute type)
+        self.out_scale = float(out_scale)
+
+    def bind(self, tensors):
+        if self.out_scale != 1.0:
+            tensors = dict(tensors)
+            for name in ("out.weight", "out.bias"):
+                if name in tensors:
+                    t = tensors[name]
+                    tensors[name] = (t.to(torch.float32) * self.out_scale).to(t.dtype)
+        super().bind(tensors)
 
     def specs(self):
         specs = {"qkv.weight": TensorSpec((self.width, self.proj_width), MATRIX, ("normal", self.init_std)),

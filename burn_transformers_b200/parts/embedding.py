@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..weights.spec import MATRIX, TensorSpec
+from ..weights.spec import MATRIX, VECTOR, TensorSpec
 from .base import Part
 from .linear import linear
 
@@ -29,6 +29,26 @@ class TokenEmbedding(Part):
             program.add_embed(ctx.tokens, ctx.positions if table is not None else None, self.t_weight, table, out32)
             return
         kernels.embed(ctx.tokens, ctx.positions, self.t_weight, table, out32, status=None, scale=self.scale)
+
+
+class StreamVectors(Part):
+    """A table of learned vectors [count, width], one of which is added to every row of the residual stream where the
+    model's run order says so (a run of layers that is repeated opens each pass with its own vector).  Kept in 32-bit:
+    the sum is part of the stream."""
+
+    def __init__(self, count: int, width: int, init_std: float = 0.02):
+        self.count, self.width, self.init_std = count, width, init_std
+
+    def specs(self):
+        return {"weight": TensorSpec((self.count, self.width), VECTOR, ("normal", self.init_std))}
+
+    def forward(self, ctx, residual, index: int):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("a vector added between layers has no phase in the fused step")
+        if not 0 <= index < self.count:
+            raise IndexError(f"vector {index} of {self.count}")
+        kernels.add_vector(residual, self.t_weight[index], n_rows=ctx.n_tokens)
 
 
 class TiedReadout(Part):

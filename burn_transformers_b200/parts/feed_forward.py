@@ -7,6 +7,8 @@ from .base import FeedForward
 from .linear import linear
 
 ACTIVATIONS = ("gelu_new", "gelu")
+# rules for the (gate, up) pair of a gated feed-forward: an activation on the gate, or the clamped rule
+PAIR_RULES = ACTIVATIONS + ("swish_clamp",)
 
 
 class DenseFeedForward(FeedForward):
@@ -45,15 +47,17 @@ class DenseFeedForward(FeedForward):
 class GatedFeedForward(FeedForward):
     """down(act(gate(x)) * up(x)), added to the residual stream; no biases.  The gate and up matrices are one product:
     `gate_up.weight` is [2 * inner, width] (stored [out, in]: the gate's rows, then up's), `down.weight` [width, inner].
-    The activation and the product of the two halves are formed in 32-bit and rounded once."""
+    The activation and the product of the two halves are formed in 32-bit and rounded once.  With the rule
+    `swish_clamp` the hidden row is g' sigmoid(1.702 g') (u' + 1), g' = min(gate x, limit), u' = up x clamped to
+    [-limit, limit]."""
 
     accepts_lazy_norm = True
 
-    def __init__(self, width: int, inner: int, activation: str = "gelu_new", *, init_std: float = 0.02,
-                 down_init_std: float | None = None):
-        if activation not in ACTIVATIONS:
-            raise ValueError(f"activation must be one of {ACTIVATIONS}, found {activation!r}")
-        self.width, self.inner, self.activation = width, inner, activation
+    def __init__(self, width: int, inner: int, activation: str = "gelu_new", *, limit: float = 0.0,
+                 init_std: float = 0.02, down_init_std: float | None = None):
+        if activation not in PAIR_RULES:
+            raise ValueError(f"activation must be one of {PAIR_RULES}, found {activation!r}")
+        self.width, self.inner, self.activation, self.limit = width, inner, activation, float(limit)
         self.init_std = init_std
         self.down_init_std = init_std if down_init_std is None else down_init_std
 
@@ -70,6 +74,6 @@ class GatedFeedForward(FeedForward):
         both = ctx.ws.take((n, 2 * self.inner), ctx.dtype)
         linear(ctx, x, self.t_gate_up_weight, None, both, m=n, w_is_nk=True)
         hidden = ctx.ws.take((n, self.inner), ctx.dtype)
-        kernels.gated_activation(both, hidden, n_rows=n, activation=self.activation)
+        kernels.gated_activation(both, hidden, n_rows=n, activation=self.activation, limit=self.limit)
         linear(ctx, hidden, self.t_down_weight, None, residual, m=n, residual=residual, w_is_nk=True)
         ctx.ws.release(mark)

@@ -1,0 +1,92 @@
+"""A feed-forward of routed experts."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import ShapeError
+from ..weights.spec import MATRIX, TensorSpec
+from .base import FeedForward
+
+
+class RoutedFeedForward(FeedForward):
+    """`n_experts` small gated feed-forwards of which every token uses `top`, and optionally one that every token uses.
+
+        s = sigmoid(W_r h)                              router, summed in 32-bit
+        experts lie in `n_groups` equal groups of neighbours; a group's score is the sum of its two largest s; only the
+        experts of the `keep` best groups can be chosen; of those the `top` largest s are
+        weight_e = s_e / (sum of the chosen s + 1e-20) * scale
+        y = sum over the chosen e of weight_e * down_e(pair(gate_e h, up_e h))  (+ shared(h))
+
+    `pair` is a rule of parts.feed_forward.PAIR_RULES (`swish_clamp` with `limit`: g' sigmoid(1.702 g') (u' + 1), g' =
+    min(g, limit), u' = u clamped to +-limit).  The (token, expert) pairs are sorted by expert on the device, the
+    experts' products run over the sorted rows (csrc/moe.cu), and the weighted results are summed per token in the order
+    of its choices; nothing is read back by the host, so the step can be recorded as a CUDA graph.
+
+    Tensors: `router.weight` [experts, width]; `in.weight` [experts * 2 * inner, width] (per expert the gate's rows,
+    then up's); `out.weight` [experts * width, inner].  `shared` is a feed-forward part of its own.
+    """
+
+    accepts_lazy_norm = False
+
+    def __init__(self, width: int, n_experts: int, top: int, inner: int, *, activation: str = "swish_clamp",
+                 limit: float = 0.0, n_groups: int = 1, keep: int = 1, scale: float = 1.0, shared: FeedForward | None = None,
+                 init_std: float = 0.02, down_init_std: float | None = None):
+        if min(width, n_experts, top, inner, n_groups, keep) <= 0:
+            raise ShapeError("routed feed-forward: sizes must be positive")
+        if n_experts % n_groups or keep > n_groups or top > keep * (n_experts // n_groups):
+            raise ShapeError(f"routed feed-forward: {n_experts} experts in {n_groups} groups of which {keep} are kept "
+                             f"cannot give {top} experts a token")
+        if n_experts > 1024 or top > 32:
+            raise ShapeError("routed feed-forward: the router kernel takes up to 1024 experts and 32 a token")
+        if activation not in kernels.PAIR_RULES:
+            raise ShapeError(f"routed feed-forward: unknown rule {activation!r}")
+        self.width, self.n_experts, self.top, self.inner = width, n_experts, top, inner
+        self.activation, self.limit = activation, float(limit)
+        self.n_groups, self.keep, self.scale, self.shared = n_groups, keep, float(scale), shared
+        self.init_std = init_std
+        self.down_init_std = inner ** -0.5 if down_init_std is None else down_init_std
+
+    def specs(self):
+        e = self.n_experts
+        return {"router.weight": TensorSpec((e, self.width), MATRIX, ("normal", self.init_std)),
+                "in.weight": TensorSpec((e * 2 * self.inner, self.width), MATRIX, ("normal", self.init_std)),
+                "out.weight": TensorSpec((e * self.width, self.inner), MATRIX, ("normal", self.down_init_std))}
+
+    def parts(self):
+        return {} if self.shared is None else {"shared": self.shared}
+
+    @property
+    def graph_safe(self):
+        return self.shared is None or self.shared.graph_safe
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.w_in = self.t_in_weight.view(self.n_experts, 2 * self.inner, self.width)
+        self.w_out = self.t_out_weight.view(self.n_experts, self.width, self.inner)
+
+    def forward(self, ctx, x, residual):
+        if getattr(ctx, "program", None) is not None:
+            from ..engine.program import ProgramUnsupported
+            raise ProgramUnsupported("routed experts have no phase in the fused step")
+        n, top, e = ctx.n_tokens, self.top, self.n_experts
+        pairs = n * top
+        mark = ctx.ws.mark()
+        ids = ctx.ws.take((n, top), torch.int32)
+        weights = ctx.ws.take((n, top), torch.float32)
+        kernels.moe_route(x, self.t_router_weight, ids, weights, n_tokens=n, top=top, n_groups=self.n_groups,
+                          keep=self.keep, scale=self.scale)
+        offsets = ctx.ws.take((e + 1,), torch.int32)
+        tile_first = ctx.ws.take((e + 1,), torch.int32)
+        order = ctx.ws.take((pairs,), torch.int32)
+        place = ctx.ws.take((pairs,), torch.int32)
+        kernels.moe_sort(ids, offsets, tile_first, order, place, pairs=pairs, n_experts=e)
+        hidden = ctx.ws.take((pairs, self.inner), ctx.dtype)
+        kernels.moe_expert(True, x, self.w_in, hidden, offsets, tile_first, order, None, pairs=pairs, top=top,
+                           activation=self.activation, limit=self.limit)
+        part = ctx.ws.take((pairs, self.width), torch.float32)
+        kernels.moe_expert(False, hidden, self.w_out, part, offsets, tile_first, order, weights, pairs=pairs, top=top)
+        kernels.moe_combine(part, place, residual, n_tokens=n, top=top)
+        ctx.ws.release(mark)
+        if self.shared is not None:
+            self.shared.forward(ctx, x, residual)

@@ -47,6 +47,16 @@ class Concat:
     sizes: tuple[int, ...] | None = None
 
 
+@dataclasses.dataclass(frozen=True)
+class PadBlocks:
+    """`source` cut along `axis` into runs of `block`, each followed by zeros up to `padded` (heads whose channels are
+    fewer than the kernels' head size; a few rows that fill a matrix up to a whole number of 16-byte pieces)."""
+    source: object
+    axis: int
+    block: int
+    padded: int
+
+
 def _flip(shape: tuple[int, ...], transposed: bool) -> tuple[int, ...]:
     if not transposed:
         return tuple(shape)
@@ -79,6 +89,13 @@ def stored_shapes(source, shape: tuple[int, ...]) -> list[tuple[str, tuple[int, 
             piece[source.axis] = size
             found += stored_shapes(part, tuple(piece))
         return found
+    if isinstance(source, PadBlocks):
+        if not 0 < source.block <= source.padded or shape[source.axis] % source.padded:
+            raise ValueError(f"runs of {source.block} padded to {source.padded} along axis {source.axis} cannot make a "
+                             f"tensor of shape {list(shape)}")
+        inner = list(shape)
+        inner[source.axis] = shape[source.axis] // source.padded * source.block
+        return stored_shapes(source.source, tuple(inner))
     raise TypeError(f"not a weight source: {source!r}")
 
 
@@ -95,6 +112,14 @@ def resolve(source, stored: dict):
         return t.narrow(source.axis, start, source.sizes[source.index])
     if isinstance(source, Concat):
         return torch.cat([resolve(part, stored) for part in source.parts], dim=source.axis)
+    if isinstance(source, PadBlocks):
+        t = resolve(source.source, stored)
+        shape = list(t.shape)
+        runs = shape[source.axis] // source.block
+        cut = t.reshape(shape[:source.axis] + [runs, source.block] + shape[source.axis + 1:])
+        full = cut.new_zeros(shape[:source.axis] + [runs, source.padded] + shape[source.axis + 1:])
+        full.narrow(source.axis + 1, 0, source.block).copy_(cut)
+        return full.reshape(shape[:source.axis] + [runs * source.padded] + shape[source.axis + 1:])
     raise TypeError(f"not a weight source: {source!r}")
 
 
