@@ -35,6 +35,7 @@ def library() -> ctypes.CDLL:
         lib.bt_attention_decode_scratch_floats.restype = c_longlong
         lib.bt_latent_attention_scratch_floats.restype = c_longlong
         lib.bt_lightning_chunked_scratch_floats.restype = c_longlong
+        lib.bt_mlstm_chunked_scratch_floats.restype = c_longlong
         lib.bt_launch_count.restype = c_longlong
         if lib.bt_abi_version() != 1:
             raise KernelError(f"{path} has an unexpected interface version")
@@ -52,7 +53,8 @@ class KernelProfile:
 
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
             "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats",
-            "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats", "bt_sink_attention_supports")
+            "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats", "bt_sink_attention_supports",
+            "bt_mlstm_chunked_scratch_floats", "bt_moe_tile_rows")
 
     def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
@@ -850,12 +852,23 @@ def add_vector(x, vec, *, n_rows):
     _check(library().bt_add_vector(_ptr(x), _ptr(vec), c_longlong(n_rows), c_int(vec.shape[0]), _stream()))
 
 
+MLSTM_CHUNK = 64      # runs of more new tokens than this take the chunked form of the matrix memory's recurrence
+
+
+def mlstm_chunked_scratch_floats(n_rows, n_seqs, max_new, n_heads, dim, vdim) -> int:
+    return int(library().bt_mlstm_chunked_scratch_floats(c_longlong(n_rows), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+                                                         c_int(dim), c_int(vdim)))
+
+
 def mlstm_scan(proj, offsets, i_bias, f_bias, cap: float, q_scale: float, s, n, m, slots, seq_start, out, *, n_seqs,
                n_heads, dim, vdim, max_new=None, scratch=None):
     """The matrix memory's recurrence over the step's tokens of every sequence (csrc/mlstm.cu).  `offsets` = channels
     of q, k, v (heads side by side) and of the input and forget gates (one channel a head) in the rows of `proj`.
     s [slots, heads, dim, vdim], n [slots, heads, dim], m [slots, heads]: 32-bit state, read and written at
-    `slots[seq]`.  out [tokens, heads * vdim] 32-bit: S^T q / (max(|n . q|, exp(-m)) + 1e-6)."""
+    `slots[seq]`.  out [tokens, heads * vdim] 32-bit: S^T q / (max(|n . q|, exp(-m)) + 1e-6).
+
+    With `max_new` (no sequence brings more tokens) above MLSTM_CHUNK and `scratch` (32-bit,
+    mlstm_chunked_scratch_floats for out's rows) the chunks of a long run are worked side by side; else token by token."""
     q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
     _need(proj, "proj", (torch.float32, torch.bfloat16))
     _need(s, "s", torch.float32, (None, n_heads, dim, vdim))
@@ -871,6 +884,17 @@ def mlstm_scan(proj, offsets, i_bias, f_bias, cap: float, q_scale: float, s, n, 
     n_rows = out.shape[0]
     _work(4.0 * n_rows * n_heads * dim * vdim, n_rows * n_heads * ((2 * dim + vdim) * proj.element_size() + 4 * vdim)
           + 8.0 * n_seqs * n_heads * dim * vdim)
+    if max_new is not None and max_new > MLSTM_CHUNK and scratch is not None:
+        need = mlstm_chunked_scratch_floats(n_rows, n_seqs, max_new, n_heads, dim, vdim)
+        if scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_cuda:
+            raise ShapeError(f"mlstm_scan: runs of {max_new} tokens need {need} floats of scratch")
+        _check(library().bt_mlstm_chunked(_ptr(proj), c_longlong(width), c_int(q_off), c_int(k_off), c_int(v_off),
+                                          c_int(i_off), c_int(f_off), _ptr(i_bias), _ptr(f_bias), c_float(cap),
+                                          c_float(q_scale), _ptr(s), _ptr(n), _ptr(m), _ptr(slots), _ptr(seq_start),
+                                          _ptr(out), c_longlong(out.shape[1]), _ptr(scratch), c_longlong(n_rows),
+                                          c_int(max_new), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
+                                          c_int(_code(proj.dtype)), _stream()))
+        return
     _check(library().bt_mlstm_scan(_ptr(proj), c_longlong(width), c_int(q_off), c_int(k_off), c_int(v_off), c_int(i_off),
                                    c_int(f_off), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale), _ptr(s),
                                    _ptr(n), _ptr(m), _ptr(slots), _ptr(seq_start), _ptr(out), c_longlong(out.shape[1]),

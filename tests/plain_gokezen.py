@@ -50,33 +50,45 @@ def window_attention(h, w, prefix, c):
     return out.reshape(T, H * vdim) @ w[prefix + "o"].T
 
 
+def memory_recurrence(q, k, v, a, b, state=None):
+    """One head: q, k [T, dim], v [T, vdim], log gates a (input) and b (forget) [T]; state (S, n, m) or None for a
+    sequence that starts.  Returns (o [T, vdim], state after the last token).
+
+        m_t = max(b_t + m_(t-1), a_t)
+        S_t = exp(b_t + m_(t-1) - m_t) S_(t-1) + exp(a_t - m_t) k_t v_t^T       (n_t the same with k_t alone)
+        o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)"""
+    T, dim = q.shape
+    S, n, m = (np.zeros((dim, v.shape[1])), np.zeros(dim), 0.0) if state is None else state
+    out = np.zeros((T, v.shape[1]))
+    for t in range(T):
+        m_new = max(b[t] + m, a[t])
+        keep, take = np.exp(b[t] + m - m_new), np.exp(a[t] - m_new)
+        S = keep * S + take * np.outer(k[t], v[t])
+        n = keep * n + take * k[t]
+        m = m_new
+        out[t] = S.T @ q[t] / (max(abs(n @ q[t]), np.exp(-m)) + 1e-6)
+    return out, (S, n, m)
+
+
+def capped_gates(x_i, x_f, cap):
+    """Log input gate and log forget gate from their pre-activations (biases already added)."""
+    return cap * np.tanh(x_i / cap), log_sigmoid(cap * np.tanh(x_f / cap))
+
+
 def matrix_memory(h, w, prefix, c, eps):
-    """Per head a matrix S (dim x vdim), a vector n (dim) and a running maximum m, all zero before the first token:
-
-        i_t = cap tanh(a_t / cap),  f_t = log sigmoid(cap tanh(b_t / cap))      (a, b: one number per head and token)
-        m_t = max(f_t + m_(t-1), i_t)
-        S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T       (n_t the same with k_t alone)
-        o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
-
-    then each head's o_t over its own root mean square, the heads side by side times a weight and a sigmoid gate."""
+    """Per head a matrix S (dim x vdim), a vector n (dim) and a running maximum m, all zero before the first token
+    (memory_recurrence), read by q = W_q h * dim^-1/2; then each head's o_t over its own root mean square, the heads side
+    by side times a weight and a sigmoid gate, then W_o."""
     T = h.shape[0]
     H, dim, vdim, cap = c["heads"], c["dim"], c["vdim"], c["gate_cap"]
     q = (h @ w[prefix + "q"].T).reshape(T, H, dim) * dim ** -0.5
     k = (h @ w[prefix + "k"].T).reshape(T, H, dim)
     v = (h @ w[prefix + "v"].T).reshape(T, H, vdim)
-    gi = cap * np.tanh((h @ w[prefix + "i"].T + w[prefix + "i.b"]) / cap)
-    gf = log_sigmoid(cap * np.tanh((h @ w[prefix + "f"].T + w[prefix + "f.b"]) / cap))
+    gi, gf = capped_gates(h @ w[prefix + "i"].T + w[prefix + "i.b"], h @ w[prefix + "f"].T + w[prefix + "f.b"], cap)
     out = np.zeros((T, H, vdim))
     for a in range(H):
-        S, n, m = np.zeros((dim, vdim)), np.zeros(dim), 0.0
-        for t in range(T):
-            m_new = max(gf[t, a] + m, gi[t, a])
-            keep, take = np.exp(gf[t, a] + m - m_new), np.exp(gi[t, a] - m_new)
-            S = keep * S + take * np.outer(k[t, a], v[t, a])
-            n = keep * n + take * k[t, a]
-            m = m_new
-            o = S.T @ q[t, a] / (max(abs(n @ q[t, a]), np.exp(-m)) + 1e-6)
-            out[t, a] = o / np.sqrt(np.mean(o * o) + eps)
+        o, _ = memory_recurrence(q[:, a], k[:, a], v[:, a], gi[:, a], gf[:, a])
+        out[:, a] = o / np.sqrt(np.mean(o * o, axis=-1, keepdims=True) + eps)
     flat = out.reshape(T, H * vdim) * w[prefix + "norm"] * sigmoid(h @ w[prefix + "g"].T)
     return flat @ w[prefix + "o"].T
 
@@ -97,8 +109,10 @@ def clamped_expert(h, w, prefix, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[prefix + "down"].T
 
 
-def route(h, router, c):
-    """(chosen experts [T, top], their weights [T, top]) of sigmoid scores, experts of the best groups only."""
+def route(h, router, c, margins=None):
+    """(chosen experts [T, top], their weights [T, top]) of sigmoid scores, experts of the best groups only.  `margins`
+    (an array [T]) is lowered, per token, to the smallest gap by which a group or an expert was preferred to the best
+    one that was left out: where it is tiny, rounding decides the choice and a comparison proves nothing."""
     E, top = c["experts"], c["top"]
     groups = c.get("groups") or {"count": 1, "keep": 1}
     scores = sigmoid(h @ router.T)
@@ -113,14 +127,21 @@ def route(h, router, c):
         allowed = np.full(E, -np.inf)
         for g in kept:
             allowed[g * size:(g + 1) * size] = scores[t, g * size:(g + 1) * size]
-        chosen[t] = np.argsort(-allowed, kind="stable")[:top]
+        ranked = np.argsort(-allowed, kind="stable")
+        chosen[t] = ranked[:top]
+        if margins is not None:
+            by_score = np.sort(group_score)[::-1]
+            if groups["keep"] < groups["count"]:
+                margins[t] = min(margins[t], by_score[groups["keep"] - 1] - by_score[groups["keep"]])
+            if top < len(kept) * size:
+                margins[t] = min(margins[t], allowed[ranked[top - 1]] - allowed[ranked[top]])
         picked = scores[t, chosen[t]]
         weights[t] = picked / (picked.sum() + 1e-20) * c["scale"]
     return chosen, weights
 
 
-def routed_feed_forward(h, w, prefix, c):
-    chosen, weights = route(h, w[prefix + "router"], c["router"])
+def routed_feed_forward(h, w, prefix, c, margins=None):
+    chosen, weights = route(h, w[prefix + "router"], c["router"], margins)
     out = np.zeros((h.shape[0], w[prefix + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, weight in zip(chosen[t], weights[t]):
@@ -130,10 +151,10 @@ def routed_feed_forward(h, w, prefix, c):
     return out
 
 
-def feed_forward(h, w, prefix, c):
+def feed_forward(h, w, prefix, c, margins=None):
     if c is None:
         return 0.0
-    return dense_feed_forward(h, w, prefix) if c["kind"] == "dense" else routed_feed_forward(h, w, prefix, c)
+    return dense_feed_forward(h, w, prefix) if c["kind"] == "dense" else routed_feed_forward(h, w, prefix, c, margins)
 
 
 def run_order(config):
@@ -148,8 +169,8 @@ def run_order(config):
     return order + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and the stream after every layer run)."""
+def forward(config, w, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one whole sequence (and the stream after every layer run).  `margins`: see route."""
     w = {k: np.asarray(v, dtype=np.float64) for k, v in w.items()}
     eps = config["norm"]["eps"]
     T = len(tokens)
@@ -160,7 +181,7 @@ def forward(config, w, tokens, return_layers=False):
         if opens is not None:
             x = x + w["loop.step"][opens]
         h = rms_norm(x, w[f"l{i}.norm1"], eps)
-        x = x + (side_by_side(h, w, f"l{i}.mix.", layer["mixer"], eps) + feed_forward(h, w, f"l{i}.mlp.", layer.get("mlp")))
+        x = x + (side_by_side(h, w, f"l{i}.mix.", layer["mixer"], eps) + feed_forward(h, w, f"l{i}.mlp.", layer.get("mlp"), margins))
         layers.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["embed"].T
     return (logits, np.stack(layers)) if return_layers else logits
