@@ -1,7 +1,7 @@
 """Decode and prefill throughput of GPT-2 (random weights, synthetic tokens) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--points all|small] [--profile]
-    python bench.py --arch sovozen [--sizes small,medium]
+    python bench.py --arch sovozen|gokezen [--sizes small,medium]
 
 A step is one decode step of a batch of 8 sequences of GPT-2 small.  The run prints one JSON line: `value` is decoded
 tokens per second, timed on the device with CUDA events over exactly K steps; `e2e` is the same through the public
@@ -374,10 +374,35 @@ def sovozen(size: str) -> dict:
             "logit_scale": 1.0, "layers": layers}
 
 
+def gokezen(size: str) -> dict:
+    """A Gokezen with as many layer runs, the width and the heads of GPT-2 `size`: every layer a windowed attention (a
+    key head for every four query heads, window 512) beside a matrix memory; feed-forwards in turn dense and routed (16
+    experts in 4 groups of which 2 are kept, 4 a token, and a shared one), each with the weights a token uses equal to
+    GPT-2's (3 x ff x width = 8 x width^2); the middle layers run twice."""
+    n_layer, width, heads = {"small": (12, 768, 12), "medium": (24, 1024, 16)}[size]
+    ff, expert_ff, shared_ff = {"small": (2048, 384, 512), "medium": (2816, 512, 768)}[size]
+    dim = 64
+    mixer = {"left": {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                      "mask": {"size": 512}}, "left_scale": 1.0,
+             "right": {"heads": heads, "dim": dim, "vdim": dim, "gate_cap": 15.0}, "right_scale": 1.0}
+    routed = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+              "router": {"experts": 16, "top": 4, "scale": 1.0, "groups": {"count": 4, "keep": 2}},
+              "shared": {"ff": shared_ff, "limit": 7.0}}
+    stored = n_layer * 2 // 3            # a third of the layer runs are second passes
+    layers = [{"type": "parallel", "mixer": mixer, "mlp": routed if i % 2 else {"kind": "dense", "ff": ff}}
+              for i in range(stored)]
+    return {"architecture": "Gokezen", "vocab": 50257, "width": width, "max_positions": 2048, "norm": {"eps": 1e-5},
+            "layers": layers, "loop": {"start": stored // 4, "stop": stored // 4 + n_layer - stored, "times": 2}}
+
+
+ARCH_PAIRS = {"sovozen": (sovozen, "gpt2", gpt2), "gokezen": (gokezen, "sovozen", sovozen)}
+
+
 def run_arch_compare(args):
-    """--arch sovozen: prefill and decode throughput of a Sovozen beside the GPT-2 of the same width and depth (random
-    weights, bfloat16), and where each spends a prefill and a decode step, kernel by kernel, against the measured
-    peaks.  One JSON line; the default workload of this file is untouched."""
+    """--arch sovozen | gokezen: prefill and decode throughput of that design beside the library's closest other
+    model at the same width and depth (GPT-2 for Sovozen, Sovozen for Gokezen; random weights, bfloat16), and where each
+    spends a prefill and a decode step, kernel by kernel, against the measured peaks.  One JSON line; the default
+    workload of this file is untouched."""
     import numpy as np
     import torch
 
@@ -389,7 +414,8 @@ def run_arch_compare(args):
         return 1
     pk = peaks()
     rng = np.random.default_rng(0)
-    report = {"arch": "sovozen", "beside": "gpt2", "dtype": "bf16", "data": "synthetic: random ids, random weights",
+    make, beside, make_beside = ARCH_PAIRS[args.arch]
+    report = {"arch": args.arch, "beside": beside, "dtype": "bf16", "data": "synthetic: random ids, random weights",
               "peaks": pk, "sizes": {}}
 
     def kernel_table(rows, steps=1):
@@ -457,7 +483,7 @@ def run_arch_compare(args):
 
     with ClockSampler() as clocks:
         for size in args.sizes.split(","):
-            report["sizes"][size] = {"sovozen": measure(sovozen(size), 50257), "gpt2": measure(gpt2(size), 50257)}
+            report["sizes"][size] = {args.arch: measure(make(size), 50257), beside: measure(make_beside(size), 50257)}
     report["clocks"] = clocks.summary()
     print(json.dumps(report))
     return 0
@@ -591,9 +617,10 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="print where a prefill and a decode step spend their time, kernel by kernel, instead")
     parser.add_argument("--model", choices=["small", "medium", "xl"], default="small", help="the model --profile looks at")
-    parser.add_argument("--arch", choices=["gpt2", "sovozen"], default="gpt2",
-                        help="sovozen: measure a Sovozen beside the GPT-2 of equal width and depth instead (see --sizes)")
-    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen: which widths (small, medium)")
+    parser.add_argument("--arch", choices=["gpt2", "sovozen", "gokezen"], default="gpt2",
+                        help="sovozen, gokezen: measure that design beside the closest other model of equal width and "
+                             "depth instead (see --sizes)")
+    parser.add_argument("--sizes", default="small,medium", help="with --arch sovozen | gokezen: which widths (small, medium)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust crate (Cargo.toml only): pip "
@@ -605,7 +632,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.arch == "sovozen":
+    if args.arch in ARCH_PAIRS:
         return run_arch_compare(args)
     return run_ours(args)
 

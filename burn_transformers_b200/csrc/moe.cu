@@ -11,8 +11,9 @@
 //   moe_expert_out  part[r] = weight(r) * down_e hidden[r]   (32-bit)
 //   moe_combine  stream[t] += sum over the token's pairs, in the order of its choices: no atomics, a fixed order.
 //
-// The products exist as 32-bit multiply-adds (float32, and every shape) and on tensor cores (bfloat16, mma.sync
-// m16n8k16 with 32-bit accumulators, K a multiple of 16).  A row's result never depends on its neighbours in the tile.
+// The products exist as 32-bit multiply-adds (float32, and every shape), on tensor cores (bfloat16, mma.sync m16n8k16
+// with 32-bit accumulators, K a multiple of 8) and, for steps with few rows an expert, as a kernel that streams every
+// expert's weights once (bfloat16).  A row's result never depends on its neighbours in the tile.
 #include "common.cuh"
 
 namespace bt {
@@ -28,6 +29,22 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 constexpr int ROUTE_WARPS = 4;
 
+// A 16-byte piece of a row as 32-bit numbers.
+__device__ __forceinline__ void load_piece(const float* p, float (&o)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ router, int n_tokens, int K, int E,
@@ -42,12 +59,40 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= n_tokens) return;
   const T* row = x + (long long)t * x_row_stride;
-  for (int e = 0; e < E; ++e) {
-    const T* w = router + (long long)e * K;
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(to_float(row[k]), to_float(w[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) score[e] = 1.f / (1.f + expf(-acc));
+  // four experts at a time: a lane takes 16-byte pieces of the token's row and of the experts' rows (element by element
+  // where K or an address does not allow pieces), sums in 32-bit, and the lanes' sums meet by shuffles
+  constexpr int V = 16 / (int)sizeof(T), EB = 4;
+  const bool pieces = K % V == 0 && x_row_stride % V == 0 && (reinterpret_cast<unsigned long long>(x) & 15) == 0 &&
+                      (reinterpret_cast<unsigned long long>(router) & 15) == 0;
+  for (int e0 = 0; e0 < E; e0 += EB) {
+    float acc[EB] = {0.f, 0.f, 0.f, 0.f};
+    if (pieces) {
+      for (int k = lane * V; k < K; k += 32 * V) {
+        float xv[V];
+        load_piece(row + k, xv);
+#pragma unroll
+        for (int j = 0; j < EB; ++j) {
+          if (e0 + j < E) {
+            float wv[V];
+            load_piece(router + (long long)(e0 + j) * K + k, wv);
+#pragma unroll
+            for (int u = 0; u < V; ++u) acc[j] = fmaf(xv[u], wv[u], acc[j]);
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float xv = to_float(row[k]);
+#pragma unroll
+        for (int j = 0; j < EB; ++j)
+          if (e0 + j < E) acc[j] = fmaf(xv, to_float(router[(long long)(e0 + j) * K + k]), acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < EB; ++j) {
+      const float z = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-z));
+    }
   }
   __syncwarp();
   for (int e = lane; e < E; e += 32) cand[e] = score[e];
@@ -336,6 +381,81 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
     }
 }
 
+// ---- the products for few rows an expert (decode steps, bfloat16) ---------------------------------------------------
+// A block: one expert and 8 output columns (each of 4 warps two columns; for the first product the gate's and up's rows
+// of a column together).  The expert's rows, 8 at a time, lie in shared memory; a warp streams its columns' weight
+// rows once per 8 rows, a lane 16-byte pieces of K, sums in 32-bit, and the lanes' sums meet by shuffles.  Every weight
+// byte is read by one warp; a block whose expert got no row ends at once.
+constexpr int MF_ROWS = 8, MF_COLS = 8, MF_KC = 2048;
+
+template <bool IN>
+__global__ void __launch_bounds__(128)
+moe_expert_few_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                      MoeArgs p) {
+  __shared__ __align__(16) __nv_bfloat16 x_s[MF_ROWS][MF_KC];
+  pdl_trigger();
+  pdl_wait();
+  const int expert = blockIdx.y;
+  const int first = p.offsets[expert], count = p.offsets[expert + 1] - first;
+  if (count == 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * MF_COLS + warp * 2;
+  const __nv_bfloat16* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
+  for (int r0 = 0; r0 < count; r0 += MF_ROWS) {
+    const int rows = min(MF_ROWS, count - r0);
+    float acc[IN ? 2 : 1][2][MF_ROWS] = {};
+    for (int k0 = 0; k0 < p.K; k0 += MF_KC) {
+      const int kc = min(MF_KC, p.K - k0);
+      __syncthreads();
+      for (int i = threadIdx.x; i < MF_ROWS * (kc / 8); i += 128) {
+        const int r = i / (kc / 8), c = (i - r * (kc / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) {
+          const long long src = IN ? p.order[first + r0 + r] / p.top : first + r0 + r;
+          v = *reinterpret_cast<const uint4*>(a + src * p.a_row_stride + k0 + c);
+        }
+        *reinterpret_cast<uint4*>(&x_s[r][c]) = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int col = 0; col < 2; ++col) {
+        const int n = n0 + col;
+        if (n >= p.N) continue;
+        for (int k = lane * 8; k < kc; k += 256) {
+          float wv[IN ? 2 : 1][8];
+          load_piece(w_e + (long long)n * p.K + k0 + k, wv[0]);
+          if (IN) load_piece(w_e + (long long)(p.N + n) * p.K + k0 + k, wv[IN ? 1 : 0]);
+#pragma unroll
+          for (int r = 0; r < MF_ROWS; ++r) {
+            float xv[8];
+            load_piece(&x_s[r][k], xv);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              acc[0][col][r] = fmaf(xv[u], wv[0][u], acc[0][col][r]);
+              if (IN) acc[IN ? 1 : 0][col][r] = fmaf(xv[u], wv[IN ? 1 : 0][u], acc[IN ? 1 : 0][col][r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int col = 0; col < 2; ++col)
+#pragma unroll
+      for (int r = 0; r < MF_ROWS; ++r) {
+        const float g = warp_sum(acc[0][col][r]);
+        const float u = IN ? warp_sum(acc[IN ? 1 : 0][col][r]) : 0.f;
+        const int n = n0 + col;
+        if (lane == 0 && r < rows && n < p.N) {
+          const long long row = first + r0 + r;
+          if (IN)
+            reinterpret_cast<__nv_bfloat16*>(out)[row * p.N + n] = __float2bfloat16_rn(gated_pair(g, u, p.act, p.limit));
+          else
+            reinterpret_cast<float*>(out)[row * p.N + n] = g * p.pair_weight[p.order[row]];
+        }
+      }
+  }
+}
+
 // stream[t, c] += sum_j part[place[t * top + j], c]
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ part, const int* __restrict__ place, float* __restrict__ stream,
@@ -404,6 +524,19 @@ extern "C" int bt_moe_expert(int first, const void* a, long long a_row_stride, c
   const int tiles = (pairs + MS_BM - 1) / MS_BM + E;      // no more row tiles than this, however the pairs fall
   BT_CHECK(tiles <= 65535, "moe_expert: %d pairs are more row tiles than a launch takes", pairs);
   const dim3 grid((N + MS_BN - 1) / MS_BN, tiles);
+  const bool pieces = dtype == kBF16 && K % 8 == 0 && a_row_stride % 8 == 0 && (unsigned long long)a % 16 == 0 &&
+                      (unsigned long long)w % 16 == 0;
+  if (pieces && tensor_cores && pairs <= 16 * E && E <= 65535) {
+    // few rows an expert (a decode step): every expert's weights streamed once per 8 of its rows
+    const dim3 few((N + MF_COLS - 1) / MF_COLS, E);
+    if (first)
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<true>, few, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    else
+      BT_PDL_OK("moe_expert", launch_pdl(moe_expert_few_kernel<false>, few, dim3(128), 0, stream, 1,
+                                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, p));
+    return 0;
+  }
   if (dtype == kBF16 && tensor_cores && K % 8 == 0 && a_row_stride % 8 == 0 && (unsigned long long)a % 16 == 0 &&
       (unsigned long long)w % 16 == 0) {
     if (first)

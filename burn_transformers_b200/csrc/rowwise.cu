@@ -33,6 +33,39 @@ rmsnorm_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* _
   }
 }
 
+// The same with a warp per run of at most 32 * NV channels: the run stays in registers, read once, no block barrier.
+template <typename TIn, typename TGate, typename TOut, int NV>
+__global__ void __launch_bounds__(128)
+rmsnorm_warp_kernel(const TIn* __restrict__ x, long long x_row_stride, const float* __restrict__ weight,
+                    const TGate* __restrict__ gate, long long gate_row_stride, TOut* __restrict__ out,
+                    long long out_row_stride, int width, int groups, long long items, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const long long r = item / groups;
+  const int first = (int)(item - r * groups) * width;
+  const TIn* src = x + r * x_row_stride + first;
+  float v[NV], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    v[i] = c < width ? to_float(src[c]) : 0.f;
+    ss = fmaf(v[i], v[i], ss);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)width + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < width) {
+      float y = v[i] * inv * weight[first + c];
+      if (gate) y *= 1.f / (1.f + expf(-to_float(gate[r * gate_row_stride + first + c])));
+      out[r * out_row_stride + first + c] = from_float<TOut>(y);
+    }
+  }
+}
+
 // dst[t, v, :] = src[t, v, :] with the pairs (2i, 2i+1), i < dims/2, turned by positions[t] * inv_freq[i]; the
 // channels from `dims` to `len` are copied.  src and dst may be the same memory.
 template <typename T>
@@ -125,7 +158,21 @@ static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGat
                           long long os, int n_rows, int width, int groups, float eps, int out_dtype,
                           cudaStream_t stream) {
   width /= groups;
-  const int threads = width >= 1024 ? 256 : (width > 64 ? 128 : 64);
+  const long long items = (long long)n_rows * groups;
+  if (width <= 1024) {
+    const dim3 wgrid((unsigned)((items + 3) / 4));
+#define BT_RW(TOUT, NV)                                                                                              \
+  BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_warp_kernel<TIn, TGate, TOUT, NV>, wgrid, dim3(128), 0, stream, 1, x, xs, w, \
+                                  gate, gs, (TOUT*)out, os, width, groups, items, eps))
+    if (out_dtype == kF32) {
+      if (width <= 128) BT_RW(float, 4); else BT_RW(float, 32);
+    } else {
+      if (width <= 128) BT_RW(__nv_bfloat16, 4); else BT_RW(__nv_bfloat16, 32);
+    }
+#undef BT_RW
+    return 0;
+  }
+  const int threads = 256;
   const dim3 grid((unsigned)n_rows * groups);
   if (out_dtype == kF32)
     BT_PDL_OK("rmsnorm", launch_pdl(rmsnorm_kernel<TIn, TGate, float>, grid, dim3(threads), 0, stream, 1, x, xs, w,

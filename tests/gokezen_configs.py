@@ -60,6 +60,13 @@ ODD = {"architecture": "Gokezen", "vocab": 257, "width": 72, "max_positions": 30
        "layers": [layer(left(2, 2, 20, 12, 33, 0.22), right(3, 12, 10, 20.0), 1.1, 0.9, moe(6, 1, 20, 1.5, 0.7, groups=(2, 1))),
                   layer(left(5, 1, 12, 28, 300, 0.3), right(1, 36, 50, 5.0), 0.7, 1.2, dense(100))]}
 
+# C: a width and sizes that are no whole 16-byte pieces anywhere, a single pass through a "repeated" run, a window of one
+# token and one longer than any sequence, one expert.
+ODDER = {"architecture": "Gokezen", "vocab": 131, "width": 52, "max_positions": 200, "norm": {"eps": 1e-5},
+         "layers": [layer(left(3, 1, 6, 10, 1, 0.4), right(2, 5, 7, 3.0), 1.0, 1.0, dense(30)),
+                    layer(left(1, 1, 14, 6, 1000, 0.25), right(1, 9, 3, 30.0), -0.5, 0.8, moe(1, 1, 12, 0.8, 1.0, shared=(10, 0.5)))],
+         "loop": {"start": 1, "stop": 2, "times": 1}}
+
 # One mechanism at a time (a scale of zero silences the other mixer; the stream still passes the layer).
 ONLY_LEFT = {"architecture": "Gokezen", "vocab": 120, "width": 64, "max_positions": 400, "norm": {"eps": 1e-5},
              "layers": [layer(left(4, 2, 16, 24, 50, 0.3), right(1, 8, 8, 10.0), 1.0, 0.0)]}
@@ -73,7 +80,7 @@ ONLY_LOOP = {"architecture": "Gokezen", "vocab": 120, "width": 64, "max_position
              "layers": [layer(left(2, 1, 16, 16, 20, 0.25), right(2, 16, 16, 10.0), 1.0, 1.0, dense(96))],
              "loop": {"start": 0, "stop": 1, "times": 4}}
 
-CONFIGS = {"mixed": MIXED, "odd": ODD, "only_left": ONLY_LEFT, "only_right": ONLY_RIGHT, "only_routed": ONLY_ROUTED,
+CONFIGS = {"mixed": MIXED, "odd": ODD, "odder": ODDER, "only_left": ONLY_LEFT, "only_right": ONLY_RIGHT, "only_routed": ONLY_ROUTED,
            "only_loop": ONLY_LOOP}
 
 

@@ -112,7 +112,7 @@ def test_memory_recurrence_over_long_runs(long_run, chunked):
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("groups, width", [(1, 96), (4, 96), (3, 30), (5, 200)])
+@pytest.mark.parametrize("groups, width", [(1, 96), (4, 96), (3, 30), (5, 200), (1, 1000), (1, 1500), (2, 2400), (3, 600)])
 def test_rms_norm_per_head_with_a_gate(out_dtype, groups, width):
     rng = np.random.default_rng(groups)
     rows = 9
