@@ -191,56 +191,65 @@ struct MlstmChunked {
   int max_chunks, col_blocks;
 };
 
+constexpr int MG_TOKENS = 2048;   // tokens whose gates lie in shared memory at a time (a multiple of the chunk)
+
 template <typename T>
 __global__ void __launch_bounds__(256) mlstm_gates_kernel(const T* __restrict__ proj, MlstmChunked c) {
+  __shared__ float a_s[MG_TOKENS], b_s[MG_TOKENS];
   const MlstmArgs& p = c.a;
   pdl_trigger();
   pdl_wait();
   const int head = blockIdx.x, seq = blockIdx.y, H = p.n_heads;
   const int first = p.seq_start[seq], n_new = p.seq_start[seq + 1] - first;
   const float bias_i = p.i_bias[head], bias_f = p.f_bias[head];
-  for (int t = threadIdx.x; t < n_new; t += blockDim.x) {
-    const T* row = proj + (long long)(first + t) * p.row_stride + head;
-    c.ga[(long long)(first + t) * H + head] = p.cap * tanhf((to_float(row[p.i_off]) + bias_i) / p.cap);
-    c.gc[(long long)(first + t) * H + head] = log_sigmoid(p.cap * tanhf((to_float(row[p.f_off]) + bias_f) / p.cap));
-  }
-  __syncthreads();
-  if (threadIdx.x >= 32) return;
-  const int lane = threadIdx.x;
+  const int lane = threadIdx.x & 31;
   const long long slot_head = (long long)p.slots[seq] * H + head;
-  float m = p.m[slot_head], m_in = m, sum = 0.f;
-  for (int t0 = 0; t0 < n_new; t0 += 32) {
-    const int chunk = t0 / MC;
-    const long long at = ((long long)seq * c.max_chunks + chunk) * H + head;
-    if (t0 % MC == 0) {
-      sum = 0.f;
-      m_in = m;
-      if (lane == 0) c.m_start[at] = m;
+  float m = p.m[slot_head], m_in = m, sum = 0.f;       // (warp 0's copies are the ones that count)
+  for (int base = 0; base < n_new; base += MG_TOKENS) {
+    const int count = min(MG_TOKENS, n_new - base);
+    __syncthreads();
+    for (int t = threadIdx.x; t < count; t += blockDim.x) {
+      const T* row = proj + (long long)(first + base + t) * p.row_stride + head;
+      const float a = p.cap * tanhf((to_float(row[p.i_off]) + bias_i) / p.cap);
+      a_s[t] = a;
+      b_s[t] = log_sigmoid(p.cap * tanhf((to_float(row[p.f_off]) + bias_f) / p.cap));
+      c.ga[(long long)(first + base + t) * H + head] = a;
     }
-    const int t = t0 + lane;
-    const bool valid = t < n_new;
-    const long long g = (long long)(first + t) * H + head;
-    // the map of token t is m -> max(m + B, A); lanes past the run hold the identity
-    float B = valid ? c.gc[g] : 0.f, A = valid ? c.ga[g] : -INFINITY;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float Bp = __shfl_up_sync(0xffffffffu, B, o), Ap = __shfl_up_sync(0xffffffffu, A, o);
-      if (lane >= o) {
-        A = fmaxf(Ap + B, A);
-        B = Bp + B;
+    __syncthreads();
+    if (threadIdx.x >= 32) continue;
+    for (int t0 = 0; t0 < count; t0 += 32) {
+      const int chunk = (base + t0) / MC;
+      const long long at = ((long long)seq * c.max_chunks + chunk) * H + head;
+      if ((base + t0) % MC == 0) {
+        sum = 0.f;
+        m_in = m;
+        if (lane == 0) c.m_start[at] = m;
       }
+      const int t = t0 + lane;
+      const bool valid = t < count;
+      // the map of token t is m -> max(m + B, A); lanes past the run hold the identity
+      float B = valid ? b_s[t] : 0.f, A = valid ? a_s[t] : -INFINITY;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float Bp = __shfl_up_sync(0xffffffffu, B, o), Ap = __shfl_up_sync(0xffffffffu, A, o);
+        if (lane >= o) {
+          A = fmaxf(Ap + B, A);
+          B = Bp + B;
+        }
+      }
+      const float m_t = fmaxf(m + B, A);
+      if (valid) {
+        const long long g = (long long)(first + base + t) * H + head;
+        c.gc[g] = sum + B;
+        c.gm[g] = m_t;
+      }
+      const int last = min(31, count - 1 - t0);
+      m = __shfl_sync(0xffffffffu, m_t, last);
+      sum += __shfl_sync(0xffffffffu, B, last);
+      if (lane == 0 && ((base + t0 + 32) % MC == 0 || base + t0 + 32 >= n_new)) c.carry[at] = expf(sum + m_in - m);
     }
-    const float m_t = fmaxf(m + B, A);
-    if (valid) {
-      c.gc[g] = sum + B;
-      c.gm[g] = m_t;
-    }
-    const int last = min(31, n_new - 1 - t0);
-    m = __shfl_sync(0xffffffffu, m_t, last);
-    sum += __shfl_sync(0xffffffffu, B, last);
-    if (lane == 0 && ((t0 + 32) % MC == 0 || t0 + 32 >= n_new)) c.carry[at] = expf(sum + m_in - m);
   }
-  if (lane == 0) p.m[slot_head] = m;
+  if (threadIdx.x == 0) p.m[slot_head] = m;
 }
 
 // grid (chunks, heads * column blocks, sequences); 256 threads as a 16 x 16 grid, thread (ty, tx) owns a 4 x 4 patch of

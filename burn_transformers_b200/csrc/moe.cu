@@ -45,7 +45,22 @@ __device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float (&o)[8]
   }
 }
 
-template <typename T>
+__device__ __forceinline__ void unpack_piece(const uint4& v, float (&o)[4]) {
+  o[0] = __uint_as_float(v.x); o[1] = __uint_as_float(v.y); o[2] = __uint_as_float(v.z); o[3] = __uint_as_float(v.w);
+}
+__device__ __forceinline__ void unpack_piece(const uint4& v, float (&o)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+
+// NP > 0: the token's row is whole 16-byte pieces, at most NP a lane; the lane keeps them in registers and asks for the
+// pieces of four experts' rows at once, so that a token costs a few trips to memory, not one per expert and piece.
+template <typename T, int NP>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __restrict__ router, int n_tokens, int K, int E,
                  int top, int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights) {
@@ -59,39 +74,54 @@ moe_route_kernel(const T* __restrict__ x, long long x_row_stride, const T* __res
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= n_tokens) return;
   const T* row = x + (long long)t * x_row_stride;
-  // four experts at a time: a lane takes 16-byte pieces of the token's row and of the experts' rows (element by element
-  // where K or an address does not allow pieces), sums in 32-bit, and the lanes' sums meet by shuffles
   constexpr int V = 16 / (int)sizeof(T), EB = 4;
-  const bool pieces = K % V == 0 && x_row_stride % V == 0 && (reinterpret_cast<unsigned long long>(x) & 15) == 0 &&
-                      (reinterpret_cast<unsigned long long>(router) & 15) == 0;
-  for (int e0 = 0; e0 < E; e0 += EB) {
-    float acc[EB] = {0.f, 0.f, 0.f, 0.f};
-    if (pieces) {
-      for (int k = lane * V; k < K; k += 32 * V) {
-        float xv[V];
-        load_piece(row + k, xv);
+  if (NP > 0) {
+    float xv[NP > 0 ? NP : 1][V];
 #pragma unroll
-        for (int j = 0; j < EB; ++j) {
-          if (e0 + j < E) {
-            float wv[V];
-            load_piece(router + (long long)(e0 + j) * K + k, wv);
+    for (int i = 0; i < NP; ++i) {
+      const int k = (lane + 32 * i) * V;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (k < K) raw = *reinterpret_cast<const uint4*>(row + k);
+      unpack_piece(raw, xv[i]);
+    }
+    for (int e0 = 0; e0 < E; e0 += EB) {
+      uint4 raw[EB][NP > 0 ? NP : 1];
 #pragma unroll
-            for (int u = 0; u < V; ++u) acc[j] = fmaf(xv[u], wv[u], acc[j]);
-          }
+      for (int j = 0; j < EB; ++j)
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          const int k = (lane + 32 * i) * V;
+          raw[j][i] = (e0 + j < E && k < K) ? *reinterpret_cast<const uint4*>(router + (long long)(e0 + j) * K + k)
+                                            : make_uint4(0, 0, 0, 0);
         }
-      }
-    } else {
-      for (int k = lane; k < K; k += 32) {
-        const float xv = to_float(row[k]);
 #pragma unroll
-        for (int j = 0; j < EB; ++j)
-          if (e0 + j < E) acc[j] = fmaf(xv, to_float(router[(long long)(e0 + j) * K + k]), acc[j]);
+      for (int j = 0; j < EB; ++j) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          float wv[V];
+          unpack_piece(raw[j][i], wv);
+#pragma unroll
+          for (int u = 0; u < V; ++u) acc = fmaf(xv[i][u], wv[u], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-acc));
       }
     }
+  } else {
+    for (int e0 = 0; e0 < E; e0 += EB) {
+      float acc[EB] = {0.f, 0.f, 0.f, 0.f};
+      for (int k = lane; k < K; k += 32) {
+        const float xs = to_float(row[k]);
 #pragma unroll
-    for (int j = 0; j < EB; ++j) {
-      const float z = warp_sum(acc[j]);
-      if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-z));
+        for (int j = 0; j < EB; ++j)
+          if (e0 + j < E) acc[j] = fmaf(xs, to_float(router[(long long)(e0 + j) * K + k]), acc[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < EB; ++j) {
+        const float z = warp_sum(acc[j]);
+        if (lane == 0 && e0 + j < E) score[e0 + j] = 1.f / (1.f + expf(-z));
+      }
     }
   }
   __syncwarp();
@@ -313,25 +343,32 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   float acc[IN ? 2 : 1][2][2][4] = {};      // [half][m tile][n tile][fragment]
   const __nv_bfloat16* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  // 16-byte pieces, 4 a row: a thread moves one piece of the rows and two (four, with both halves) of the weights per
+  // K piece; the next K piece's are asked for before this one's products, and land in registers meanwhile
+  constexpr int HALVES = IN ? 2 : 1;
+  const int pr = threadIdx.x >> 2, pc = (threadIdx.x & 3) * 8;
+  const int a_src = src_row[pr];
+  uint4 ra, rw[HALVES][2];
+  auto fetch = [&](int k0) {
+    ra = (a_src >= 0 && k0 + pc < p.K) ? *reinterpret_cast<const uint4*>(a + (long long)a_src * p.a_row_stride + k0 + pc) : zero;
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + pr + 32 * j;
+        rw[h][j] = (n < p.N && k0 + pc < p.K)
+                       ? *reinterpret_cast<const uint4*>(w_e + (long long)(h * p.N + n) * p.K + k0 + pc) : zero;
+      }
+  };
+  fetch(0);
   for (int k0 = 0; k0 < p.K; k0 += MM_BK) {
-    // 16-byte pieces: 4 a row
-    for (int i = threadIdx.x; i < MM_BM * 4; i += 128) {
-      const int r = i >> 2, c = (i & 3) * 8;
-      const int src = src_row[r];
-      uint4 v = zero;
-      if (src >= 0 && k0 + c < p.K) v = *reinterpret_cast<const uint4*>(a + (long long)src * p.a_row_stride + k0 + c);
-      *reinterpret_cast<uint4*>(&a_s[r][c]) = v;
-    }
-    for (int i = threadIdx.x; i < MM_BN * 4; i += 128) {
-      const int n = i >> 2, c = (i & 3) * 8;
-      const bool in = n0 + n < p.N && k0 + c < p.K;
-      *reinterpret_cast<uint4*>(&w_s[0][n][c]) =
-          in ? *reinterpret_cast<const uint4*>(w_e + (long long)(n0 + n) * p.K + k0 + c) : zero;
-      if (IN)
-        *reinterpret_cast<uint4*>(&w_s[IN ? 1 : 0][n][c]) =
-            in ? *reinterpret_cast<const uint4*>(w_e + (long long)(p.N + n0 + n) * p.K + k0 + c) : zero;
-    }
+    *reinterpret_cast<uint4*>(&a_s[pr][pc]) = ra;
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) *reinterpret_cast<uint4*>(&w_s[h][pr + 32 * j][pc]) = rw[h][j];
     __syncthreads();
+    if (k0 + MM_BK < p.K) fetch(k0 + MM_BK);
 #pragma unroll
     for (int kk = 0; kk < MM_BK; kk += 16) {
       uint32_t af[2][4];
@@ -484,15 +521,28 @@ extern "C" int bt_moe_route(const void* x, long long x_row_stride, const void* r
   if (n_tokens == 0) return 0;
   const dim3 grid((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), block(ROUTE_WARPS * 32);
   const size_t smem = (size_t)ROUTE_WARPS * 3 * E * sizeof(float);
-  if (dtype == kF32)
-    BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<float>, grid, block, smem, stream, 1, (const float*)x, x_row_stride,
-                                      (const float*)router, n_tokens, K, E, top, n_groups, keep, scale, ids, weights));
-  else if (dtype == kBF16)
-    BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream, 1,
-                                      (const __nv_bfloat16*)x, x_row_stride, (const __nv_bfloat16*)router, n_tokens, K, E,
-                                      top, n_groups, keep, scale, ids, weights));
-  else
+  // pieces of 16 bytes a lane holds of a token's row: 1, 2 or 4 (rows of up to 128 pieces); 0: element by element
+  auto pieces_of = [&](int elem) {
+    const int v = 16 / elem;
+    if (K % v || x_row_stride % v || (unsigned long long)x % 16 || (unsigned long long)router % 16) return 0;
+    const int per_lane = (K / v + 31) / 32;
+    return per_lane <= 1 ? 1 : per_lane <= 2 ? 2 : per_lane <= 4 ? 4 : 0;
+  };
+#define BT_ROUTE(T, NP)                                                                                              \
+  BT_PDL_OK("moe_route", launch_pdl(moe_route_kernel<T, NP>, grid, block, smem, stream, 1, (const T*)x, x_row_stride, \
+                                    (const T*)router, n_tokens, K, E, top, n_groups, keep, scale, ids, weights))
+  if (dtype == kF32) {
+    const int np = pieces_of(4);
+    if (np == 1) BT_ROUTE(float, 1); else if (np == 2) BT_ROUTE(float, 2); else if (np == 4) BT_ROUTE(float, 4);
+    else BT_ROUTE(float, 0);
+  } else if (dtype == kBF16) {
+    const int np = pieces_of(2);
+    if (np == 1) BT_ROUTE(__nv_bfloat16, 1); else if (np == 2) BT_ROUTE(__nv_bfloat16, 2);
+    else if (np == 4) BT_ROUTE(__nv_bfloat16, 4); else BT_ROUTE(__nv_bfloat16, 0);
+  } else {
     return fail("moe_route: unknown dtype %d", dtype);
+  }
+#undef BT_ROUTE
   return 0;
 }
 
