@@ -35,6 +35,13 @@ struct MlstmArgs {
   float* out;
   long long out_row_stride;
   int n_heads, dim, vdim, cols;
+  // with `mixed`: a block holds all value channels of its head, and instead of o the kernel leaves
+  // o / rms(o) * norm_w * sigmoid(gate) (the gate's channels at g_off of the rows of proj) in `mixed`, in proj's type
+  const float* norm_w;
+  float eps;
+  int g_off;
+  void* mixed;
+  long long mixed_row_stride;
 };
 
 template <typename T, int DPT, int SPLIT>
@@ -47,6 +54,7 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const T* __restrict__ p
   float* keep_s = v_s + ML_TOKENS * cols;     // [ML_TOKENS] exp(b + m_old - m_new)
   float* take_s = keep_s + ML_TOKENS;         // [ML_TOKENS] exp(a - m_new)
   float* floor_s = take_s + ML_TOKENS;        // [ML_TOKENS] exp(-m_new)
+  float* red_s = floor_s + ML_TOKENS;         // [33] for sums over the block
   pdl_trigger();
   pdl_wait();
   const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * cols;
@@ -120,9 +128,19 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const T* __restrict__ p
         o += __shfl_xor_sync(0xffffffffu, o, x);
         nq += __shfl_xor_sync(0xffffffffu, nq, x);
       }
-      if (owns && part == 0)
-        p.out[(long long)(first + t0 + t) * p.out_row_stride + (long long)head * vdim + col] =
-            o / (fmaxf(fabsf(nq), floor_s[t]) + 1e-6f);
+      const float read = o / (fmaxf(fabsf(nq), floor_s[t]) + 1e-6f);
+      if (p.mixed) {
+        const float ss = block_sum(owns && part == 0 ? read * read : 0.f, red_s);
+        if (owns && part == 0) {
+          const long long row = first + t0 + t;
+          const int ch = head * vdim + col;
+          const float gate = to_float(proj[row * p.row_stride + p.g_off + ch]);
+          const float y = read / sqrtf(ss / (float)vdim + p.eps) * p.norm_w[ch] / (1.f + expf(-gate));
+          reinterpret_cast<T*>(p.mixed)[row * p.mixed_row_stride + ch] = from_float<T>(y);
+        }
+      } else if (owns && part == 0) {
+        p.out[(long long)(first + t0 + t) * p.out_row_stride + (long long)head * vdim + col] = read;
+      }
     }
   }
   if (owns) {
@@ -146,13 +164,21 @@ static int launch_mlstm(const T* proj, MlstmArgs p, int n_seqs, cudaStream_t str
   else if (p.dim <= 64) { dpt = 8; split = 8; }
   else if (p.dim <= 128) { dpt = 16; split = 8; }
   else { dpt = 32; split = 8; }
+  if (p.mixed && p.vdim > 256 / split) {      // a whole head a block: 64 value channels, more key channels a lane
+    split = 4;
+    dpt = p.dim <= 64 ? 16 : 32;
+  }
   p.cols = 256 / split < p.vdim ? 256 / split : p.vdim;   // value channels per block
   const dim3 grid((p.vdim + p.cols - 1) / p.cols, p.n_heads, n_seqs), block(256);
-  const size_t smem = (size_t)ML_TOKENS * (2 * p.dim + p.cols + 3) * sizeof(float);
+  BT_CHECK(!p.mixed || grid.x == 1, "mlstm_scan: a head of %d x %d does not fit one block, the norm cannot be fused", p.dim,
+           p.vdim);
+  const size_t smem = (size_t)(ML_TOKENS * (2 * p.dim + p.cols + 3) + 33) * sizeof(float);
 #define BT_ML(DPT, SPLIT) \
   BT_PDL_OK("mlstm_scan", launch_pdl(mlstm_scan_kernel<T, DPT, SPLIT>, grid, block, smem, stream, 1, proj, p))
   if (dpt == 8 && split == 4) BT_ML(8, 4);
   else if (dpt == 8) BT_ML(8, 8);
+  else if (dpt == 16 && split == 4) BT_ML(16, 4);
+  else if (dpt == 32 && split == 4) BT_ML(32, 4);
   else if (dpt == 16) BT_ML(16, 8);
   else BT_ML(32, 8);
 #undef BT_ML
@@ -557,9 +583,16 @@ static int launch_mlstm_chunked(const T* proj, MlstmArgs p, float* scratch, long
 
 }  // namespace bt
 
+// Whether bt_mlstm_scan can hold a whole head in one block, and so apply the per-head norm and the gate itself.
+extern "C" int bt_mlstm_scan_fuses(int dim, int vdim) { return vdim <= 32 || (vdim <= 64 && dim <= 128); }
+
+// norm_w .. mixed_row_stride: null / 0, or (where bt_mlstm_scan_fuses) the per-head RMS norm's weight [heads * vdim], its
+// eps, the channel of the output gate in the rows of proj, and where the normed and gated rows go (proj's type); `out`
+// is then not written.
 extern "C" int bt_mlstm_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, int i_off, int f_off,
                              const float* i_bias, const float* f_bias, float cap, float q_scale, float* s, float* n,
                              float* m, const int* slots, const int* seq_start, float* out, long long out_row_stride,
+                             const float* norm_w, float eps, int g_off, void* mixed, long long mixed_row_stride,
                              int n_seqs, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream) {
   using namespace bt;
   BT_CHECK(n_heads > 0 && dim > 0 && dim <= 256 && vdim > 0 && n_seqs >= 0 && n_seqs <= 65535 && n_heads <= 65535,
@@ -573,6 +606,9 @@ extern "C" int bt_mlstm_scan(const void* proj, long long row_stride, int q_off, 
   p.i_bias = i_bias; p.f_bias = f_bias; p.cap = cap; p.q_scale = q_scale;
   p.s = s; p.n = n; p.m = m; p.slots = slots; p.seq_start = seq_start; p.out = out; p.out_row_stride = out_row_stride;
   p.n_heads = n_heads; p.dim = dim; p.vdim = vdim; p.cols = 0;
+  BT_CHECK(mixed == nullptr || (norm_w != nullptr && bt_mlstm_scan_fuses(dim, vdim)),
+           "mlstm_scan: the norm of heads of %d x %d cannot be fused", dim, vdim);
+  p.norm_w = norm_w; p.eps = eps; p.g_off = g_off; p.mixed = mixed; p.mixed_row_stride = mixed_row_stride;
   if (dtype == kF32) return launch_mlstm<float>((const float*)proj, p, n_seqs, stream);
   if (dtype == kBF16) return launch_mlstm<__nv_bfloat16>((const __nv_bfloat16*)proj, p, n_seqs, stream);
   return fail("mlstm_scan: unknown dtype %d", dtype);
@@ -604,6 +640,7 @@ extern "C" int bt_mlstm_chunked(const void* proj, long long row_stride, int q_of
   p.i_bias = i_bias; p.f_bias = f_bias; p.cap = cap; p.q_scale = q_scale;
   p.s = s; p.n = n; p.m = m; p.slots = slots; p.seq_start = seq_start; p.out = out; p.out_row_stride = out_row_stride;
   p.n_heads = n_heads; p.dim = dim; p.vdim = vdim; p.cols = 64;
+  p.norm_w = nullptr; p.eps = 0.f; p.g_off = 0; p.mixed = nullptr; p.mixed_row_stride = 0;
   if (dtype == kF32) return launch_mlstm_chunked<float>((const float*)proj, p, scratch, n_rows, max_new, n_seqs, stream);
   if (dtype == kBF16)
     return launch_mlstm_chunked<__nv_bfloat16>((const __nv_bfloat16*)proj, p, scratch, n_rows, max_new, n_seqs, stream);

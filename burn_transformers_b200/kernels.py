@@ -861,14 +861,19 @@ def mlstm_chunked_scratch_floats(n_rows, n_seqs, max_new, n_heads, dim, vdim) ->
 
 
 def mlstm_scan(proj, offsets, i_bias, f_bias, cap: float, q_scale: float, s, n, m, slots, seq_start, out, *, n_seqs,
-               n_heads, dim, vdim, max_new=None, scratch=None):
+               n_heads, dim, vdim, max_new=None, scratch=None, norm=None) -> bool:
     """The matrix memory's recurrence over the step's tokens of every sequence (csrc/mlstm.cu).  `offsets` = channels
     of q, k, v (heads side by side) and of the input and forget gates (one channel a head) in the rows of `proj`.
     s [slots, heads, dim, vdim], n [slots, heads, dim], m [slots, heads]: 32-bit state, read and written at
     `slots[seq]`.  out [tokens, heads * vdim] 32-bit: S^T q / (max(|n . q|, exp(-m)) + 1e-6).
 
     With `max_new` (no sequence brings more tokens) above MLSTM_CHUNK and `scratch` (32-bit,
-    mlstm_chunked_scratch_floats for out's rows) the chunks of a long run are worked side by side; else token by token."""
+    mlstm_chunked_scratch_floats for out's rows) the chunks of a long run are worked side by side; else token by token.
+
+    `norm` = (weight [heads * vdim] 32-bit, eps, channel of the output gate in proj's rows, mixed [tokens, heads * vdim]
+    of proj's type): where the token-by-token kernel can hold a whole head in one block (mlstm_scan_fuses) it leaves
+    out / rms(out per head) * weight * sigmoid(gate) in `mixed`, writes no `out`, and the call returns True; otherwise
+    `out` is written and the caller norms."""
     q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
     _need(proj, "proj", (torch.float32, torch.bfloat16))
     _need(s, "s", torch.float32, (None, n_heads, dim, vdim))
@@ -894,12 +899,26 @@ def mlstm_scan(proj, offsets, i_bias, f_bias, cap: float, q_scale: float, s, n, 
                                           _ptr(out), c_longlong(out.shape[1]), _ptr(scratch), c_longlong(n_rows),
                                           c_int(max_new), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim),
                                           c_int(_code(proj.dtype)), _stream()))
-        return
+        return False
+    fuse = norm is not None and mlstm_scan_fuses(dim, vdim)
+    weight, eps, g_off, mixed = norm if fuse else (None, 0.0, 0, None)
+    if fuse:
+        _need(weight, "norm weight", torch.float32, (n_heads * vdim,))
+        _need(mixed, "mixed", proj.dtype, (None, n_heads * vdim))
+        if mixed.shape[0] < n_rows or g_off < 0 or g_off + n_heads * vdim > width:
+            raise ShapeError("mlstm_scan: the gate's channels leave the rows of proj, or mixed is too short")
     _check(library().bt_mlstm_scan(_ptr(proj), c_longlong(width), c_int(q_off), c_int(k_off), c_int(v_off), c_int(i_off),
                                    c_int(f_off), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale), _ptr(s),
                                    _ptr(n), _ptr(m), _ptr(slots), _ptr(seq_start), _ptr(out), c_longlong(out.shape[1]),
-                                   c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), c_int(_code(proj.dtype)),
-                                   _stream()))
+                                   _ptr(weight), c_float(eps), c_int(g_off), _ptr(mixed),
+                                   c_longlong(mixed.shape[1] if fuse else 0), c_int(n_seqs), c_int(n_heads), c_int(dim),
+                                   c_int(vdim), c_int(_code(proj.dtype)), _stream()))
+    return fuse
+
+
+def mlstm_scan_fuses(dim: int, vdim: int) -> bool:
+    """Whether the token-by-token kernel holds a whole head of this size in one block (and can norm and gate it)."""
+    return bool(library().bt_mlstm_scan_fuses(c_int(dim), c_int(vdim)))
 
 
 def moe_route(x, router, ids, weights, *, n_tokens, top, n_groups=1, keep=1, scale=1.0):

@@ -90,12 +90,14 @@ class MatrixMemory(Mixer):
             # long runs of new tokens: the chunks of a run are worked side by side (csrc/mlstm.cu)
             scratch = ctx.ws.take((kernels.mlstm_chunked_scratch_floats(n, ctx.n_seqs, ctx.max_new, self.n_heads, self.dim,
                                                                         self.vdim),), torch.float32)
-        kernels.mlstm_scan(proj, (self.q_off, self.k_off, self.v_off, self.i_off, self.f_off), self.t_i_bias, self.t_f_bias,
+        mixed = ctx.ws.take((n, self.v_width), ctx.dtype)
+        normed = kernels.mlstm_scan(proj, (self.q_off, self.k_off, self.v_off, self.i_off, self.f_off), self.t_i_bias, self.t_f_bias,
                            self.gate_cap, self.dim ** -0.5, ctx.cache.state(entry, "s"), ctx.cache.state(entry, "n"),
                            ctx.cache.state(entry, "m"), ctx.slots, ctx.seq_start, read, n_seqs=ctx.n_seqs,
-                           n_heads=self.n_heads, dim=self.dim, vdim=self.vdim, max_new=ctx.max_new, scratch=scratch)
-        mixed = ctx.ws.take((n, self.v_width), ctx.dtype)
-        kernels.rmsnorm(read, self.norm_scaled, mixed, self.eps, n_rows=n, gate=proj[:, self.g_off:self.g_off + self.v_width],
-                        groups=self.n_heads)
+                           n_heads=self.n_heads, dim=self.dim, vdim=self.vdim, max_new=ctx.max_new, scratch=scratch,
+                                    norm=(self.norm_scaled, self.eps, self.g_off, mixed))
+        if not normed:       # (long runs, and heads too large for one block of the token-by-token kernel)
+            kernels.rmsnorm(read, self.norm_scaled, mixed, self.eps, n_rows=n, gate=proj[:, self.g_off:self.g_off + self.v_width],
+                            groups=self.n_heads)
         linear(ctx, mixed, self.t_out_weight, None, residual, m=n, residual=residual, w_is_nk=True)
         ctx.ws.release(mark)

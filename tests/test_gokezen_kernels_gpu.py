@@ -76,6 +76,47 @@ def test_memory_recurrence(dtype, heads, dim, vdim, chunked):
     assert float(s[1].abs().sum()) == 0 and float(s[4].abs().sum()) == 0      # slots of no sequence stay untouched
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 32, 48), (1, 64, 64), (2, 100, 64), (3, 200, 32), (2, 8, 5), (1, 48, 72),
+                                              (1, 130, 40)])
+def test_memory_recurrence_with_the_norm_and_gate_inside(dtype, heads, dim, vdim):
+    """Where a block holds a whole head, the token-by-token kernel norms each head's read-out and gates it itself."""
+    rng = np.random.default_rng(dim + vdim)
+    lengths, slots, cap, eps = [1, 20, 1, 7], [2, 0, 1, 3], 9.0, 1e-5
+    width = 2 * heads * dim + 2 * heads * vdim + 2 * heads
+    offs = (0, heads * dim, 2 * heads * dim, 2 * heads * dim + 2 * heads * vdim, 2 * heads * dim + 2 * heads * vdim + heads)
+    g_off = 2 * heads * dim + heads * vdim
+    total = sum(lengths)
+    proj = rounded(rng.standard_normal((total, width)), dtype)
+    i_bias, f_bias = np.zeros(heads), np.full(heads, 2.0)
+    weight = rounded(1.0 + 0.3 * rng.standard_normal(heads * vdim), "float32")
+    s = torch.zeros((4, heads, dim, vdim), device=DEV)
+    n = torch.zeros((4, heads, dim), device=DEV)
+    m = torch.zeros((4, heads), device=DEV)
+    out = torch.full((total, heads * vdim), 7.0, device=DEV)
+    mixed = torch.full((total + 1, heads * vdim), 3.0, dtype=DT[dtype], device=DEV)
+    starts = np.concatenate([[0], np.cumsum(lengths)])
+    fused = kernels.mlstm_scan(dev(proj, DT[dtype]), offs, dev(i_bias), dev(f_bias), cap, dim ** -0.5, s, n, m, ints(slots),
+                               ints(starts), out, n_seqs=len(lengths), n_heads=heads, dim=dim, vdim=vdim, max_new=max(lengths),
+                               norm=(dev(weight), eps, g_off, mixed))
+    assert fused == kernels.mlstm_scan_fuses(dim, vdim) == (vdim <= 32 or (vdim <= 64 and dim <= 128))
+    if not fused:
+        assert float((mixed.float() - 3.0).abs().sum()) == 0 and float((out - 7.0).abs().min()) > 0
+        return
+    got = mixed.float().cpu().double().numpy()
+    assert np.all(got[total] == 3.0) and float((out - 7.0).abs().sum()) == 0
+    for r, (lo, hi) in enumerate(zip(starts[:-1], starts[1:])):
+        for a in range(heads):
+            ga, gb = plain.capped_gates(proj[lo:hi, offs[3] + a] + i_bias[a], proj[lo:hi, offs[4] + a] + f_bias[a], cap)
+            o, _ = plain.memory_recurrence(proj[lo:hi, a * dim:(a + 1) * dim] * dim ** -0.5,
+                                           proj[lo:hi, offs[1] + a * dim:offs[1] + (a + 1) * dim],
+                                           proj[lo:hi, offs[2] + a * vdim:offs[2] + (a + 1) * vdim], ga, gb)
+            want = (o / np.sqrt((o * o).mean(-1, keepdims=True) + eps) * weight[a * vdim:(a + 1) * vdim]
+                    * plain.sigmoid(proj[lo:hi, g_off + a * vdim:g_off + (a + 1) * vdim]))
+            err = np.abs(got[lo:hi, a * vdim:(a + 1) * vdim] - want).max() / np.abs(want).max()
+            assert err < (2e-4 if dtype == "float32" else 1e-2), (r, a, err)
+
+
 @pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("long_run", [128, 130, 517])
 def test_memory_recurrence_over_long_runs(long_run, chunked):
