@@ -153,6 +153,21 @@ add_vector_kernel(float* __restrict__ x, const float* __restrict__ vec, long lon
     x[i] += vec[i % width];
 }
 
+// x += a (+ b) (+ c), element by element, in this order: what branches of a layer that ran side by side left in buffers
+// of their own joins the 32-bit stream
+__global__ void __launch_bounds__(256)
+add_rows_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c,
+                long long n) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] + a[i];
+    if (b) v += b[i];
+    if (c) v += c[i];
+    x[i] = v;
+  }
+}
+
 template <typename TIn, typename TGate>
 static int launch_rmsnorm(const TIn* x, long long xs, const float* w, const TGate* gate, long long gs, void* out,
                           long long os, int n_rows, int width, int groups, float eps, int out_dtype,
@@ -268,5 +283,14 @@ extern "C" int bt_add_vector(float* x, const float* vec, long long n_rows, int w
   const long long total = n_rows * width;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   BT_PDL_OK("add_vector", launch_pdl(add_vector_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, vec, n_rows, width));
+  return 0;
+}
+
+extern "C" int bt_add_rows(float* x, const float* a, const float* b, const float* c, long long n, cudaStream_t stream) {
+  using namespace bt;
+  BT_CHECK(n >= 0 && a != nullptr, "add_rows: bad arguments");
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  BT_PDL_OK("add_rows", launch_pdl(add_rows_kernel, dim3(blocks), dim3(256), 0, stream, 1, x, a, b, c, n));
   return 0;
 }

@@ -29,6 +29,7 @@ class Workspace:
         self.frozen = False       # set while a CUDA graph is captured or replayed: addresses must not move
         self._retired: list[torch.Tensor] = []
         self._moves = 0           # how often the buffer has been replaced by a larger one
+        self.hold = False         # set while parts of a layer run side by side on several streams: `release` waits
 
     def reset(self) -> None:
         self.offset = 0
@@ -43,6 +44,8 @@ class Workspace:
         step's own stream (later launches on that stream come after it); a part that hands work to a second stream
         must not release what that work reads.  If the buffer was replaced meanwhile, nothing is given back."""
         moves, offset = mark
+        if self.hold:
+            return      # (work on another stream may still read what would be handed out again)
         if moves == self._moves and offset <= self.offset:
             self.offset = offset
 

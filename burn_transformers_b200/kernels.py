@@ -852,6 +852,21 @@ def add_vector(x, vec, *, n_rows):
     _check(library().bt_add_vector(_ptr(x), _ptr(vec), c_longlong(n_rows), c_int(vec.shape[0]), _stream()))
 
 
+def add_rows(x, addends, *, n_rows):
+    """x[:n_rows] += addends[0] (+ addends[1]) (+ addends[2]), in this order; contiguous 32-bit [rows, width] tensors."""
+    if not 1 <= len(addends) <= 3:
+        raise ShapeError(f"add_rows: one to three addends, not {len(addends)}")
+    _need(x, "x", torch.float32)
+    for t in addends:
+        _need(t, "addend", torch.float32, (None, x.shape[1]))
+        if t.shape[0] < n_rows:
+            raise ShapeError(f"add_rows: {n_rows} rows asked of an addend of {t.shape[0]}")
+    if x.shape[0] < n_rows:
+        raise ShapeError(f"add_rows: {n_rows} rows asked of x[{x.shape[0]}]")
+    a, b, c = (list(addends) + [None, None])[:3]
+    _check(library().bt_add_rows(_ptr(x), _ptr(a), _ptr(b), _ptr(c), c_longlong(n_rows * x.shape[1]), _stream()))
+
+
 MLSTM_CHUNK = 64      # runs of more new tokens than this take the chunked form of the matrix memory's recurrence
 
 

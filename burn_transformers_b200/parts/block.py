@@ -1,6 +1,9 @@
 """Arrangements of norms, a mixer and a feed-forward in one layer."""
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from .base import Block, FeedForward, Mixer, Norm
 
 
@@ -60,9 +63,62 @@ class ParallelBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self.parts().values())
 
+    # Steps of at most this many tokens (decode steps) run the layer's independent parts side by side: each part but
+    # the first on a stream of its own, adding into a zeroed buffer of its own; when all are done, one kernel adds the
+    # buffers to the stream in a fixed order.  Such a step is a chain of short kernels, and its time is the length of the
+    # longest chain, not the number of kernels.  Longer steps fill the GPU with every kernel and run in order.
+    side_by_side_up_to = 64
+    _streams: dict = {}
+
+    def _branches(self, entry, owns_cache):
+        """The parts of the layer that need nothing of one another, as calls (ctx, x, target)."""
+        mixers = list(self.mixer.parts().values()) if hasattr(self.mixer, "left") else [self.mixer]
+        found = [lambda ctx, x, target, m=m: m.forward(ctx, x, target, entry, owns_cache) for m in mixers]
+        ff = self.feed_forward
+        if ff is not None and hasattr(ff, "forward_routed") and ff.shared is not None:
+            found += [ff.forward_routed, ff.shared.forward]
+        elif ff is not None:
+            found.append(ff.forward)
+        return found
+
+    @classmethod
+    def _sides(cls, device, count):
+        from ..engine.step import SideWork
+        have = cls._streams.setdefault(torch.device(device), [])
+        while len(have) < count:
+            have.append(SideWork(device))
+        return have[:count]
+
     def forward(self, ctx, residual, entry, owns_cache=True):
         # (both sublayers read the same rows, so the norm hands out real rows, never a handle for one product)
+        n = ctx.n_tokens
+        branches = self._branches(entry, owns_cache)
+        if (n > self.side_by_side_up_to or len(branches) < 2 or len(branches) > 4 or residual.device.type != "cuda"
+                or getattr(ctx, "program", None) is not None):
+            x = self.norm.forward(ctx, residual, ctx.dtype, lazy=False)
+            for branch in branches:
+                branch(ctx, x, residual)
+            return
+        mark = ctx.ws.mark()
         x = self.norm.forward(ctx, residual, ctx.dtype, lazy=False)
-        self.mixer.forward(ctx, x, residual, entry, owns_cache)
-        if self.feed_forward is not None:
-            self.feed_forward.forward(ctx, x, residual)
+        sides = self._sides(residual.device, len(branches) - 1)
+        # no piece of scratch is handed out twice while the branches run, and nothing is left on the step's own second
+        # stream that reads a branch's scratch after the layer has given it back
+        held, ctx.ws.hold = ctx.ws.hold, True
+        step_side, ctx.side = getattr(ctx, "side", None), None
+        buffers = []
+        try:
+            for side, branch in zip(sides, branches[1:]):
+                target = ctx.ws.take((n, residual.shape[1]), torch.float32)
+                side.fork()
+                with side.stream_context():
+                    target.zero_()
+                    branch(ctx, x, target)
+                buffers.append(target)
+            branches[0](ctx, x, residual)
+        finally:
+            for side in sides:
+                side.join()
+            ctx.ws.hold, ctx.side = held, step_side
+        kernels.add_rows(residual, buffers, n_rows=n)
+        ctx.ws.release(mark)

@@ -66,6 +66,12 @@ class RoutedFeedForward(FeedForward):
         self.w_out = self.t_out_weight.view(self.n_experts, self.width, self.inner)
 
     def forward(self, ctx, x, residual):
+        self.forward_routed(ctx, x, residual)
+        if self.shared is not None:
+            self.shared.forward(ctx, x, residual)
+
+    def forward_routed(self, ctx, x, residual):
+        """The routed experts alone (the shared one is a feed-forward of its own and may run beside them)."""
         if getattr(ctx, "program", None) is not None:
             from ..engine.program import ProgramUnsupported
             raise ProgramUnsupported("routed experts have no phase in the fused step")
@@ -88,5 +94,3 @@ class RoutedFeedForward(FeedForward):
         kernels.moe_expert(False, hidden, self.w_out, part, offsets, tile_first, order, weights, pairs=pairs, top=top)
         kernels.moe_combine(part, place, residual, n_tokens=n, top=top)
         ctx.ws.release(mark)
-        if self.shared is not None:
-            self.shared.forward(ctx, x, residual)
