@@ -63,11 +63,14 @@ class ParallelBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self.parts().values())
 
-    # Steps of at most this many tokens (decode steps) run the layer's independent parts side by side: each part but
-    # the first on a stream of its own, adding into a zeroed buffer of its own; when all are done, one kernel adds the
-    # buffers to the stream in a fixed order.  Such a step is a chain of short kernels, and its time is the length of the
-    # longest chain, not the number of kernels.  Longer steps fill the GPU with every kernel and run in order.
-    side_by_side_up_to = 64
+    # Steps of at most this many tokens run the layer's independent parts side by side: each part but the first on a
+    # stream of its own, adding into a zeroed buffer of its own; when all are done, one kernel adds the buffers to the
+    # stream in a fixed order.  A decode step is a chain of short kernels, and its time is the length of the longest
+    # chain, not the number of kernels (Gokezen of 12 x 768 at 8 sequences: 0.96 to 0.70 ms); prompts of a few thousand
+    # tokens still gain where a part's kernels leave multiprocessors idle (2 x 1,024 tokens: 3.84 to 3.36 ms; 8 x 512:
+    # 5.86 to 5.68 ms).  Longer steps fill the GPU with every kernel and run in order; the scratch a layer holds while
+    # its parts run grows with the step.
+    side_by_side_up_to = 4096
     _streams: dict = {}
 
     def _branches(self, entry, owns_cache):
