@@ -454,7 +454,10 @@ def run_arch_compare(args):
                         engine.release(s)
             st = spread(samples)
             out[f"decode_b{batch}_ctx512"] = {"ms_per_step": st, "tokens_per_s": batch / st["median"] * 1e3}
-        # kernel by kernel, launched directly
+        # kernel by kernel, launched directly and one after another (a layer's parts not side by side on streams of their
+        # own, where a design has that: a kernel's own time, not its time beside others)
+        from burn_transformers_b200.parts.block import ParallelBlock
+        side_by_side, ParallelBlock.side_by_side_up_to = ParallelBlock.side_by_side_up_to, 0
         for warm in range(2):
             prompts = [rng.integers(0, vocab, PREFILL_TOKENS // 2 - 1 - warm).tolist() for _ in range(2)]
             slots = [engine.new_sequence() for _ in prompts]
@@ -475,6 +478,7 @@ def run_arch_compare(args):
             for _ in range(8):
                 step()
         out["decode_b8_kernels"] = kernel_table(prof.summary(), steps=8)
+        ParallelBlock.side_by_side_up_to = side_by_side
         for s in slots:
             engine.release(s)
         del engine

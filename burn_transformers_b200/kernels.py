@@ -54,7 +54,7 @@ class KernelProfile:
     SKIP = ("bt_last_error", "bt_launch_count", "bt_abi_version", "bt_tensor_map", "bt_decode_flow_plan",
             "bt_decode_flow_phase_bytes", "bt_attention_decode_scratch_floats", "bt_latent_attention_scratch_floats",
             "bt_latent_attention_rows", "bt_lightning_chunked_scratch_floats", "bt_sink_attention_supports",
-            "bt_mlstm_chunked_scratch_floats", "bt_moe_tile_rows")
+            "bt_mlstm_chunked_scratch_floats", "bt_moe_tile_rows", "bt_mlstm_scan_fuses")
 
     def __init__(self, context_hint: int | None = None):
         self.records = []          # (name, start event, stop event, flops, bytes)
