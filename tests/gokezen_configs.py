@@ -67,6 +67,13 @@ ODDER = {"architecture": "Gokezen", "vocab": 131, "width": 52, "max_positions": 
                     layer(left(1, 1, 14, 6, 1000, 0.25), right(1, 9, 3, 30.0), -0.5, 0.8, moe(1, 1, 12, 0.8, 1.0, shared=(10, 0.5)))],
          "loop": {"start": 1, "stop": 2, "times": 1}}
 
+# D: head sizes the attention kernels take by other routes: 80 (no tensor-core prompt kernel), 112 (run as 128), 144 (beyond the
+# tensor-core decode kernel), each with a window and shared key heads.
+HEADS = {"architecture": "Gokezen", "vocab": 150, "width": 80, "max_positions": 300, "norm": {"eps": 1e-5},
+         "layers": [layer(left(4, 2, 72, 80, 70, 0.12), right(1, 16, 16, 10.0), 1.0, 0.5),
+                    layer(left(2, 1, 100, 90, 130, 0.1), right(1, 16, 16, 10.0), 1.0, 0.5, dense(64)),
+                    layer(left(2, 2, 136, 20, 33, 0.09), right(1, 16, 16, 10.0), 1.0, 0.5)]}
+
 # One mechanism at a time (a scale of zero silences the other mixer; the stream still passes the layer).
 ONLY_LEFT = {"architecture": "Gokezen", "vocab": 120, "width": 64, "max_positions": 400, "norm": {"eps": 1e-5},
              "layers": [layer(left(4, 2, 16, 24, 50, 0.3), right(1, 8, 8, 10.0), 1.0, 0.0)]}
@@ -80,7 +87,7 @@ ONLY_LOOP = {"architecture": "Gokezen", "vocab": 120, "width": 64, "max_position
              "layers": [layer(left(2, 1, 16, 16, 20, 0.25), right(2, 16, 16, 10.0), 1.0, 1.0, dense(96))],
              "loop": {"start": 0, "stop": 1, "times": 4}}
 
-CONFIGS = {"mixed": MIXED, "odd": ODD, "odder": ODDER, "only_left": ONLY_LEFT, "only_right": ONLY_RIGHT, "only_routed": ONLY_ROUTED,
+CONFIGS = {"mixed": MIXED, "odd": ODD, "odder": ODDER, "heads": HEADS, "only_left": ONLY_LEFT, "only_right": ONLY_RIGHT, "only_routed": ONLY_ROUTED,
            "only_loop": ONLY_LOOP}
 
 

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 TOL = {"float32": 1e-4, "bfloat16": 4e-2}
 # lengths around the borders of a page (64), of the recurrence's staging (16) and of the windows
-LENGTHS = {"mixed": [1, 2, 7, 8, 39, 41, 64, 65, 101, 129, 260], "odd": [1, 33, 34, 64, 130], "odder": [1, 2, 66, 150],
+LENGTHS = {"mixed": [1, 2, 7, 8, 39, 41, 64, 65, 101, 129, 260], "odd": [1, 33, 34, 64, 130], "odder": [1, 2, 66, 150], "heads": [1, 70, 71, 200],
            "only_left": [1, 5, 50, 51, 64, 140], "only_right": [1, 5, 64, 97, 200], "only_routed": [1, 5, 64, 97],
            "only_loop": [1, 21, 64, 97]}
 
