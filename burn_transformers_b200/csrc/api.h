@@ -127,12 +127,40 @@ int bt_lightning_chunked(const void* proj, long long row_stride, int q_off, int 
                          cudaStream_t stream);
 int bt_rmsnorm(const void* x, int x_dtype, long long x_row_stride, const float* weight, const void* gate, int gate_dtype,
                long long gate_row_stride, void* out, int out_dtype, long long out_row_stride, int n_rows, int width,
-               float eps, cudaStream_t stream);
+               int groups, float eps, cudaStream_t stream);
 int bt_rotary_interleaved(const void* src, long long src_row_stride, int src_vec_stride, void* dst,
                           long long dst_row_stride, int dst_vec_stride, const int* positions, const float* inv_freq,
                           int n_tokens, int n_vecs, int len, int dims, int dtype, cudaStream_t stream);
-int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, int dtype, cudaStream_t stream);
+int bt_gated_activation(const void* x, void* out, long long n_rows, int inner, int act, float limit, int dtype,
+                        cudaStream_t stream);
 int bt_scale(float* x, long long n, float scale, cudaStream_t stream);
+// The matrix memory with exponential gates (csrc/mlstm.cu), routed experts (csrc/moe.cu), and the row-wise kernels they
+// added (csrc/rowwise.cu).
+int bt_mlstm_scan_fuses(int dim, int vdim);
+int bt_mlstm_scan(const void* proj, long long row_stride, int q_off, int k_off, int v_off, int i_off, int f_off,
+                  const float* i_bias, const float* f_bias, float cap, float q_scale, float* s, float* n, float* m,
+                  const int* slots, const int* seq_start, float* out, long long out_row_stride, const float* norm_w,
+                  float eps, int g_off, void* mixed, long long mixed_row_stride, int n_seqs, int n_heads, int dim, int vdim,
+                  int dtype, cudaStream_t stream);
+long long bt_mlstm_chunked_scratch_floats(long long n_rows, int n_seqs, int max_new, int n_heads, int dim, int vdim);
+int bt_mlstm_chunked(const void* proj, long long row_stride, int q_off, int k_off, int v_off, int i_off, int f_off,
+                     const float* i_bias, const float* f_bias, float cap, float q_scale, float* s, float* n, float* m,
+                     const int* slots, const int* seq_start, float* out, long long out_row_stride, float* scratch,
+                     long long n_rows, int max_new, int n_seqs, int n_heads, int dim, int vdim, int dtype,
+                     cudaStream_t stream);
+int bt_moe_route(const void* x, long long x_row_stride, const void* router, int n_tokens, int K, int E, int top,
+                 int n_groups, int keep, float scale, int* ids, float* weights, int dtype, cudaStream_t stream);
+int bt_moe_tile_rows();
+int bt_moe_sort(const int* ids, int total, int E, int* offsets, int* tile_first, int* order, int* place,
+                cudaStream_t stream);
+int bt_moe_expert(int first, const void* a, long long a_row_stride, const void* w, void* out, const int* offsets,
+                  const int* tile_first, const int* order, const float* pair_weight, int pairs, int E, int top, int K,
+                  int N, int act, float limit, int tensor_cores, int dtype, cudaStream_t stream);
+int bt_moe_combine(const float* part, const int* place, float* stream_rows, long long n_tokens, int top, int width,
+                   cudaStream_t stream);
+int bt_add_vector(float* x, const float* vec, long long n_rows, int width, cudaStream_t stream);
+int bt_add_rows(float* x, const float* a, const float* b, const float* c, long long n, cudaStream_t stream);
+
 int bt_logit_edits(float* logits, long long row_stride, const int* rows, const int* tokens, const float* vals,
                    int n_edits, int vocab, cudaStream_t stream);
 }
