@@ -313,8 +313,16 @@ moe_expert_simt_kernel(const T* __restrict__ a, const T* __restrict__ w, void* _
 
 // ---- the products on tensor cores (bfloat16) -----------------------------------------------------------------------
 // A block: 32 rows x 64 columns (both halves of the pair for the first product), 4 warps, each 32 rows x 16 columns; K in
-// pieces of 32 through shared memory (rows padded to 40 elements: fragment loads fall into different banks).
-constexpr int MM_BM = 32, MM_BN = 64, MM_BK = 32, MM_LD = MM_BK + 8;
+// pieces of 32 through a ring of three shared-memory stages filled by cp.async (rows padded to 40 elements: fragment
+// loads fall into different banks).
+constexpr int MM_BM = 32, MM_BN = 64, MM_BK = 32, MM_LD = MM_BK + 8, MM_STAGES = 3;
+
+// 16 bytes from global to shared memory without passing registers; `real` false copies no source bytes and fills zeros.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool real) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = real ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -326,8 +334,9 @@ template <bool IN>
 __global__ void __launch_bounds__(128)
 moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                       MoeArgs p) {
-  __shared__ __align__(16) __nv_bfloat16 a_s[MM_BM][MM_LD];
-  __shared__ __align__(16) __nv_bfloat16 w_s[IN ? 2 : 1][MM_BN][MM_LD];
+  constexpr int HALVES = IN ? 2 : 1;
+  __shared__ __align__(16) __nv_bfloat16 a_s[MM_STAGES][MM_BM][MM_LD];
+  __shared__ __align__(16) __nv_bfloat16 w_s[MM_STAGES][HALVES][MM_BN][MM_LD];
   __shared__ int src_row[MM_BM];
   pdl_trigger();
   pdl_wait();
@@ -340,51 +349,52 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-  float acc[IN ? 2 : 1][2][2][4] = {};      // [half][m tile][n tile][fragment]
-  const __nv_bfloat16* w_e = w + (long long)expert * (IN ? 2 : 1) * p.N * p.K;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
+  float acc[HALVES][2][2][4] = {};      // [half][m tile][n tile][fragment]
+  const __nv_bfloat16* w_e = w + (long long)expert * HALVES * p.N * p.K;
   // 16-byte pieces, 4 a row: a thread moves one piece of the rows and two (four, with both halves) of the weights per
-  // K piece; the next K piece's are asked for before this one's products, and land in registers meanwhile
-  constexpr int HALVES = IN ? 2 : 1;
+  // K piece, by cp.async into a ring of MM_STAGES K pieces: while one piece is multiplied, the next two are in flight
+  // (a piece outside the rows, the columns or K is filled with zeros: a copy of no source bytes)
   const int pr = threadIdx.x >> 2, pc = (threadIdx.x & 3) * 8;
   const int a_src = src_row[pr];
-  uint4 ra, rw[HALVES][2];
-  auto fetch = [&](int k0) {
-    ra = (a_src >= 0 && k0 + pc < p.K) ? *reinterpret_cast<const uint4*>(a + (long long)a_src * p.a_row_stride + k0 + pc) : zero;
+  auto issue = [&](int stage, int k0) {
+    if (k0 < p.K) {
+      const bool in_k = k0 + pc < p.K;
+      const bool ok = a_src >= 0 && in_k;
+      cp_async_16(&a_s[stage][pr][pc], ok ? a + (long long)a_src * p.a_row_stride + k0 + pc : a, ok);
 #pragma unroll
-    for (int h = 0; h < HALVES; ++h)
+      for (int h = 0; h < HALVES; ++h)
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int n = n0 + pr + 32 * j;
-        rw[h][j] = (n < p.N && k0 + pc < p.K)
-                       ? *reinterpret_cast<const uint4*>(w_e + (long long)(h * p.N + n) * p.K + k0 + pc) : zero;
-      }
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + pr + 32 * j;
+          const bool okw = n < p.N && in_k;
+          cp_async_16(&w_s[stage][h][pr + 32 * j][pc], okw ? w_e + (long long)(h * p.N + n) * p.K + k0 + pc : w_e, okw);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");      // (an empty group keeps the count of groups in step)
   };
-  fetch(0);
+#pragma unroll
+  for (int st = 0; st < MM_STAGES - 1; ++st) issue(st, st * MM_BK);
+  int stage = 0;
   for (int k0 = 0; k0 < p.K; k0 += MM_BK) {
-    *reinterpret_cast<uint4*>(&a_s[pr][pc]) = ra;
-#pragma unroll
-    for (int h = 0; h < HALVES; ++h)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) *reinterpret_cast<uint4*>(&w_s[h][pr + 32 * j][pc]) = rw[h][j];
-    __syncthreads();
-    if (k0 + MM_BK < p.K) fetch(k0 + MM_BK);
+    asm volatile("cp.async.wait_group %0;" ::"n"(MM_STAGES - 2) : "memory");
+    __syncthreads();      // this piece has landed for every thread, and the piece multiplied last is free again
+    issue((stage + MM_STAGES - 1) % MM_STAGES, k0 + (MM_STAGES - 1) * MM_BK);
 #pragma unroll
     for (int kk = 0; kk < MM_BK; kk += 16) {
       uint32_t af[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const __nv_bfloat16* base = &a_s[mt * 16 + gid][kk + tig * 2];
+        const __nv_bfloat16* base = &a_s[stage][mt * 16 + gid][kk + tig * 2];
         af[mt][0] = *reinterpret_cast<const uint32_t*>(base);
         af[mt][1] = *reinterpret_cast<const uint32_t*>(base + 8 * MM_LD);
         af[mt][2] = *reinterpret_cast<const uint32_t*>(base + 8);
         af[mt][3] = *reinterpret_cast<const uint32_t*>(base + 8 * MM_LD + 8);
       }
 #pragma unroll
-      for (int h = 0; h < (IN ? 2 : 1); ++h)
+      for (int h = 0; h < HALVES; ++h)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          const __nv_bfloat16* base = &w_s[h][warp * 16 + nt * 8 + gid][kk + tig * 2];
+          const __nv_bfloat16* base = &w_s[stage][h][warp * 16 + nt * 8 + gid][kk + tig * 2];
           uint32_t bf[2];
           bf[0] = *reinterpret_cast<const uint32_t*>(base);
           bf[1] = *reinterpret_cast<const uint32_t*>(base + 8);
@@ -392,8 +402,9 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* 
           for (int mt = 0; mt < 2; ++mt) mma_bf16_16816(acc[h][mt][nt], af[mt], bf);
         }
     }
-    __syncthreads();
+    stage = (stage + 1) % MM_STAGES;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
