@@ -146,6 +146,22 @@ def test_long_decoding_from_the_first_token(case, dtype):
     assert_close({(long, p): row for (_, p), row in got.items()}, ref, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layers_parts_in_order_and_side_by_side(case, dtype, monkeypatch):
+    """Steps of up to some thousand tokens run a layer's independent parts side by side on streams of their own, longer
+    ones in order: both ways give the plain implementation's logits, for prompts, decoding and batches."""
+    from burn_transformers_b200.parts.block import ParallelBlock
+    name, folder, seqs, ref = case
+    if name not in ("mixed", "odd", "only_loop"):
+        pytest.skip("runs on three configurations")
+    for up_to in (0, 10 ** 9):
+        monkeypatch.setattr(ParallelBlock, "side_by_side_up_to", up_to)
+        engine = engine_for(folder, dtype)
+        for got in (replay.whole(engine, seqs), replay.tail_one_by_one(engine, seqs, tail=20),
+                    replay.batches(engine, seqs, [list(range(len(seqs)))[:4]], [max(1, len(s) // 2) for s in seqs])):
+            assert_close(got, ref, dtype, note=f"side by side up to {up_to}: ")
+
+
 def test_a_released_slot_starts_from_an_empty_state(case):
     """A sequence that takes over a slot finds neither the old memory nor the old keys."""
     _, folder, seqs, ref = case

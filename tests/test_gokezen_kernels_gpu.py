@@ -118,7 +118,7 @@ def test_memory_recurrence_with_the_norm_and_gate_inside(dtype, heads, dim, vdim
 
 
 @pytest.mark.parametrize("chunked", [False, True])
-@pytest.mark.parametrize("long_run", [128, 130, 517])
+@pytest.mark.parametrize("long_run", [128, 130, 517, 2200])
 def test_memory_recurrence_over_long_runs(long_run, chunked):
     """Runs longer than a chunk, forget gates close to one: what the first tokens wrote is still read at the end."""
     rng = np.random.default_rng(long_run)
